@@ -1,0 +1,303 @@
+"""Benchmark of the gdn_chunk forward pass.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--path P]
+
+One "step" is one forward pass over one batch of synthetic input.  The default workload is the
+one the headline metric is quoted on: B=1, S=8192, Hq=Hk=16, Hv=32, D=128, chunk 64, bf16, with a
+random initial state.  With N > 1 (launched by torchrun, one rank per GPU) every rank runs that
+workload on its own batch element: the (batch, value-head) sequences are independent, so the path
+shards with no communication ("weak" scaling, global batch = N).  `--workload throughput` shards
+B=64, S=4096 over the ranks instead.
+
+Prints ONE JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM, timed with CUDA
+events around each step, an L2 flush between steps, max over ranks.  `e2e` is the same metric
+through the public Python API with pinned HOST buffers: host->device copies of all inputs and
+device->host copies of the output and final state inside the timed region.  `cpu_baseline` times
+the CPU oracle (the C restatement of the reference's chunked torch function) on this box's host
+cores.  `--impl reference` prints that CPU arm as its own line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "gdn_chunk_fwd_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def flops_per_token(Hq, Hv, C=64, D=128):
+    """Dense products at 64x64x128 tile granularity; Q K^T and K K^T once per qk head."""
+    return Hq * 4 * C * D + Hv * (6 * C * D + 6 * D * D)
+
+
+def bytes_per_token(Hq, Hv, gate_bytes=4):
+    """Every input read once, the output written once (state I/O is added per sequence)."""
+    return Hq * 512 + Hv * 512 + Hv * 2 * gate_bytes
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"]))}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                r = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                    "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                if r.returncode == 0 and r.stdout.strip():
+                    self.rows.append([c.strip() for c in r.stdout.strip().splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            try:
+                sm.append(float(row[0]))
+                mx.append(float(row[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, val in zip(names, row[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_arm(workload, seed, min_seconds=10.0, max_reps=12):
+    """Time the CPU oracle (chunked form, all host threads) on the whole workload, repeated."""
+    from gdn_qsa_sm80_b200.synthetic import make_inputs
+    from oracle import c_oracle
+    from gdn_qsa_sm80_b200.synthetic import WORKLOADS
+    w = WORKLOADS[workload]
+    S = min(w.S, 16384)                       # bounded sample: at most 16384 tokens per run
+    B = max(1, min(w.B, 16384 // S))
+    whole = (S == w.S and B == w.B)
+    q, k, v, g, beta, h0 = make_inputs(w, seed=seed, B=B, S=S)
+    x = [t.float().numpy() for t in (q, k, v, g, beta)]
+    h = None if h0 is None else h0.numpy()
+    threads = c_oracle.max_threads()
+    c_oracle.chunk_f32(*x, initial_state=h)   # warm-up (page faults, thread pool)
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < max_reps and (time.perf_counter() - t_start < min_seconds or len(times) < 3):
+        t0 = time.perf_counter()
+        c_oracle.chunk_f32(*x, initial_state=h)
+        times.append(time.perf_counter() - t0)
+    tokens = q.shape[0] * q.shape[1]
+    med = statistics.median(times)
+    return {"value": tokens / med, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{'whole workload' if whole else f'B={B} S={S} slice of the workload'} ({tokens} tokens) x "
+                      f"{len(times)} runs, median; C restatement of the "
+                      f"reference's chunked torch function, fp32, OpenMP over (batch, head)",
+            "ms_per_step": med * 1e3}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="default", choices=["default", "short_batch", "throughput", "long_context"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "fused_nv64", "fused_nv32"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    from gdn_qsa_sm80_b200.synthetic import WORKLOADS
+    w = WORKLOADS[args.workload]
+    cfg = {"workload": f"{w.name}: B={w.B} S={w.S} Hq={w.Hq} Hv={w.Hv} D=128 chunk=64 bf16 h0={w.h0}",
+           "l2": "flushed between timed steps (256 MiB write)", "path": args.path}
+
+    if args.impl == "reference":
+        # CPU arm: the reference's own implementation of this path is a torch function that cannot travel
+        # to the GPU box; its C restatement (pinned against it by golden vectors) is timed instead.
+        if rank != 0:
+            return
+        base = cpu_arm(args.workload, args.seed, min_seconds=max(5.0, 0.5 * args.steps))
+        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": cfg,
+                "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    from gdn_qsa_sm80 import gdn_chunk
+    from gdn_qsa_sm80_b200 import _lib
+    from gdn_qsa_sm80_b200.gdn_chunk_interface import check_device_status
+    from gdn_qsa_sm80_b200.synthetic import make_inputs
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU path for the operator")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- this rank's share of the workload ------------------------------------------------------------
+    if args.workload == "default" or w.B < world:
+        B_local, total_tokens, scaling = w.B, w.B * w.S * world, "weak"       # one whole workload per rank
+        cfg["sharding"] = f"{world} independent batch elements, one per GPU, no communication"
+    else:
+        assert w.B % world == 0, "batch must divide over the ranks"
+        B_local, total_tokens, scaling = w.B // world, w.B * w.S, "strong"
+        cfg["sharding"] = f"batch split {world} ways ({B_local} per GPU), no communication"
+    q, k, v, g, beta, h0 = make_inputs(w, seed=args.seed + rank, B=B_local)
+    host = [t.pin_memory() for t in (q, k, v, g, beta)] + [None if h0 is None else h0.pin_memory()]
+    d_in = [None if t is None else t.to(dev, non_blocking=True) for t in host]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    torch.cuda.synchronize()
+
+    def step():
+        return gdn_chunk(d_in[0], d_in[1], d_in[2], d_in[3], d_in[4], output_final_state=True,
+                         initial_state=d_in[5], path=args.path)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    check_device_status(dev)
+
+    # ---- device-resident timing ---------------------------------------------------------------------------
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    launches0 = _lib.kernel_launches()
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        for a, b in ev:
+            flush.zero_()
+            a.record()
+            step()
+            b.record()
+        barrier()
+    launches = _lib.kernel_launches() - launches0
+    check_device_status(dev)
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    total_ms = sum(step_ms)
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = total_tokens / (ms_per_step * 1e-3)
+
+    # ---- end to end through the public API with host buffers ------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        out_host = torch.empty((B_local, w.S, w.Hv, 128), dtype=torch.bfloat16).pin_memory()
+        st_host = torch.empty((B_local, w.Hv, 128, 128), dtype=torch.float32).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in host if t is not None)
+        d2h = out_host.numel() * 2 + st_host.numel() * 4
+
+        def e2e_step():
+            dd = [None if t is None else t.to(dev, non_blocking=True) for t in host]
+            o, s = gdn_chunk(dd[0], dd[1], dd[2], dd[3], dd[4], output_final_state=True, initial_state=dd[5],
+                             path=args.path)
+            out_host.copy_(o, non_blocking=True)
+            st_host.copy_(s, non_blocking=True)
+
+        n_e2e = max(3, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b.record()
+        barrier()
+        e2e_ms = a.elapsed_time(b)
+        if world > 1:
+            t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        e2e = {"value": total_tokens / (e2e_ms / n_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "steps": n_e2e}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant (here: the only) kernel, per launch on one GPU ---------------------------
+    peaks, peak_kind = load_peaks()
+    tokens_local = B_local * w.S
+    kernel_s = statistics.median(step_ms) * 1e-3
+    fl = flops_per_token(w.Hq, w.Hv) * tokens_local
+    by = bytes_per_token(w.Hq, w.Hv) * tokens_local + B_local * w.Hv * 65536 * (2 if w.h0 != "zeros" else 1)
+    tf = fl / kernel_s / 1e12
+    roofline = {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": tf / peaks["bf16_tflops"], "traffic": None,
+                "peak_kind": f"{peak_kind} (burst cuBLAS bf16)",
+                "algorithmic_flops_per_launch": fl,
+                "hbm": {"achieved": by / kernel_s / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": by / kernel_s / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes_per_launch": by},
+                "kernel_ms_median": kernel_s * 1e3}
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks.summary(),
+            "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline}
+    if world == 1 and not args.no_cpu_baseline:
+        base = cpu_arm(args.workload, args.seed)
+        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,86 @@
+"""ctypes binding of ``lib/libgdn_chunk_sm100.so`` (the C ABI in ``include/gdn_chunk_sm100.h``).
+
+The library is the only implementation: when it has not been built, loading raises and every
+operator call fails loudly.  There is no fallback path of any kind.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libgdn_chunk_sm100.so")
+
+GDN_OK = 0
+GDN_ERR_BAD_ARGUMENT = 1
+GDN_ERR_SCRATCH = 2
+GDN_ERR_CUDA = 3
+GDN_ERR_DRIVER = 4
+GDN_ERR_DEVICE = 5
+
+GATE_BF16 = 0
+GATE_F32 = 1
+
+PATH_AUTO = 0
+PATH_SIMT = 1
+PATH_FUSED_NV64 = 2
+PATH_FUSED_NV32 = 3
+PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "fused_nv64": PATH_FUSED_NV64, "fused_nv32": PATH_FUSED_NV32}
+
+# Every symbol the public header declares (checked by the CPU tests).
+EXPORTS = (
+    "gdn_chunk_scratch_bytes",
+    "gdn_chunk_fwd_sm100",
+    "gdn_chunk_read_status",
+    "gdn_chunk_error_string",
+    "gdn_chunk_kernel_launches",
+    "gdn_umma_probe",
+)
+
+_lib = None
+
+
+class GdnLibraryError(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raise if it is missing (build it with
+    ``python -m gdn_qsa_sm80_b200.build``)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise GdnLibraryError(
+            f"{LIB_PATH} is missing: build it with `python -m gdn_qsa_sm80_b200.build` "
+            "(sm_100a only; there is no fallback implementation)")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    lib.gdn_chunk_scratch_bytes.argtypes = [ci, ci, ci, ci, ci]
+    lib.gdn_chunk_scratch_bytes.restype = sz
+    lib.gdn_chunk_fwd_sm100.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, vp]
+    lib.gdn_chunk_fwd_sm100.restype = ci
+    lib.gdn_chunk_read_status.argtypes = [vp, vp, ctypes.POINTER(ci)]
+    lib.gdn_chunk_read_status.restype = ci
+    lib.gdn_chunk_error_string.argtypes = [ci]
+    lib.gdn_chunk_error_string.restype = ctypes.c_char_p
+    lib.gdn_chunk_kernel_launches.argtypes = []
+    lib.gdn_chunk_kernel_launches.restype = ctypes.c_ulonglong
+    lib.gdn_umma_probe.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp]
+    lib.gdn_umma_probe.restype = ci
+    _lib = lib
+    return lib
+
+
+def error_string(status: int) -> str:
+    return load().gdn_chunk_error_string(int(status)).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != GDN_OK:
+        raise GdnLibraryError(f"{what}: {error_string(status)} (status {status})")
+
+
+def kernel_launches() -> int:
+    return int(load().gdn_chunk_kernel_launches())

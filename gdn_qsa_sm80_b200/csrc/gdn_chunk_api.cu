@@ -1,0 +1,136 @@
+// C ABI of the library (see include/gdn_chunk_sm100.h): argument checks, TMA descriptor
+// encoding through the driver entry point, path selection, status word handling.
+#include <cuda.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "../../include/gdn_chunk_sm100.h"
+#include "gdn_common.cuh"
+
+namespace gdn {
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+int encode_tma_bf16(void* tmap_out, const void* base, int rank, const unsigned long long* dims,
+                    const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return 1;
+    cuuint64_t gdim[5], gstr[4];
+    cuuint32_t bx[5], es[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = 1;
+    }
+    for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+    const CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                        : CU_TENSOR_MAP_SWIZZLE_NONE;
+    const CUresult r = fn(static_cast<CUtensorMap*>(tmap_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
+                          const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace gdn
+
+using namespace gdn;
+
+extern "C" {
+
+size_t gdn_chunk_scratch_bytes(int B, int S, int Hq, int Hv, int path) {
+    (void)B; (void)S; (void)Hq; (void)Hv; (void)path;
+    return 256;   // the device status word, padded
+}
+
+int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                        const float* h0, void* out, float* hT, void* scratch, size_t scratch_bytes,
+                        int B, int S, int Hq, int Hv, int gate_dtype, int path, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
+    if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
+    if (path < GDN_PATH_AUTO || path > GDN_PATH_FUSED_NV32) return GDN_ERR_BAD_ARGUMENT;
+    if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u) ||
+        scratch_bytes < gdn_chunk_scratch_bytes(B, S, Hq, Hv, path))
+        return GDN_ERR_SCRATCH;
+    if (cudaMemsetAsync(scratch, 0, 256, stream) != cudaSuccess) return GDN_ERR_CUDA;
+    if (S == 0) {   // nothing to scan: the final state is the initial state
+        if (hT) {
+            const size_t bytes = static_cast<size_t>(B) * Hv * kD * kD * sizeof(float);
+            const cudaError_t e = h0 ? cudaMemcpyAsync(hT, h0, bytes, cudaMemcpyDeviceToDevice, stream)
+                                     : cudaMemsetAsync(hT, 0, bytes, stream);
+            if (e != cudaSuccess) return GDN_ERR_CUDA;
+        }
+        return GDN_OK;
+    }
+    if (!q || !k || !v || !g || !beta || !out) return GDN_ERR_BAD_ARGUMENT;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(h0) || !aligned16(hT))
+        return GDN_ERR_BAD_ARGUMENT;
+
+    Problem p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k = static_cast<const __nv_bfloat16*>(k);
+    p.v = static_cast<const __nv_bfloat16*>(v);
+    p.g = g;
+    p.beta = beta;
+    p.h0 = h0;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.hT = hT;
+    p.status = static_cast<int*>(scratch);
+    p.B = B; p.S = S; p.Hq = Hq; p.Hv = Hv;
+    p.gate_f32 = gate_dtype == GDN_GATE_F32;
+
+    if (path == GDN_PATH_SIMT) return launch_simt(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
+    int nv;
+    if (path == GDN_PATH_FUSED_NV64) nv = 64;
+    else if (path == GDN_PATH_FUSED_NV32) nv = 32;
+    else nv = (static_cast<long long>(B) * Hv * 2 >= 148) ? 64 : 32;   // fill the 148 SMs when B*Hv is small
+    return launch_fused(p, nv, stream);
+}
+
+int gdn_chunk_read_status(const void* scratch, void* stream_, int* device_status) {
+    if (!scratch || !device_status) return GDN_ERR_BAD_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int v = 0;
+    if (cudaMemcpyAsync(&v, scratch, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return GDN_ERR_CUDA;
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return GDN_ERR_CUDA;
+    *device_status = v;
+    return v == 0 ? GDN_OK : GDN_ERR_DEVICE;
+}
+
+const char* gdn_chunk_error_string(int status) {
+    switch (status) {
+        case GDN_OK: return "ok";
+        case GDN_ERR_BAD_ARGUMENT: return "bad argument (shape, alignment, dtype or path)";
+        case GDN_ERR_SCRATCH: return "scratch buffer missing, misaligned or too small";
+        case GDN_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
+        case GDN_ERR_DRIVER: return "driver rejected a TMA tensor-map description";
+        case GDN_ERR_DEVICE: return "a kernel gave up on a bounded wait (device status word is non-zero)";
+        default: return "unknown status";
+    }
+}
+
+unsigned long long gdn_chunk_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

@@ -1,0 +1,148 @@
+"""Python API of the sm_100a gdn_chunk forward, mirroring the reference project's
+``gdn_qsa_sm80/gdn_chunk_interface.py`` (same names, argument order and error behaviour).
+
+Differences from the reference, all additive:
+  * ``initial_state`` keyword (fp32 or bf16 ``[B,Hv,128,128]``) and an fp32 ``final_state``,
+    as in the reference's torch definition (``reference/gdn_chunk_ref.py:20-31``);
+  * ``GDN_CHUNK`` is 64 (the reference's CUDA path uses 16, its torch definition 64);
+  * g and beta may be bf16 or fp32;
+  * the result is exact for every gate distribution (the reference's production fast path
+    is an approximation that holds only under strong decay, ``csrc/gdn_chunk/gdn_ops.cu:845-848``).
+
+PyTorch is used only for device memory and the current stream; all arithmetic happens in the
+CUDA library behind the C ABI.  There is no CPU or eager fallback.
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import _lib
+
+__all__ = ["gdn_chunk", "gdn_chunk_twolevel", "gdn_chunk_reference", "GDN_D", "GDN_CHUNK"]
+
+GDN_D = 128      # head dim (compile-time constant in the kernels)
+GDN_CHUNK = 64   # intra-chunk size (compile-time constant)
+
+_scratch = {}
+
+
+def _check_inputs(q, k, v, g, beta):
+    # same checks and messages as the reference's _check_inputs (gdn_chunk_interface.py:19-32)
+    if q.dim() != 4 or q.size(3) != GDN_D:
+        raise ValueError(f"q must be [B,S,Hk,{GDN_D}], got {tuple(q.shape)}")
+    if k.shape != q.shape:
+        raise ValueError(f"k must match q, got q={tuple(q.shape)} k={tuple(k.shape)}")
+    B, S, Hk, _ = q.shape
+    if v.dim() != 4 or v.size(3) != GDN_D or v.shape[:2] != (B, S):
+        raise ValueError(f"v must be [B,S,Hv,{GDN_D}], got {tuple(v.shape)}")
+    Hv = v.size(2)
+    if g.shape != (B, S, Hv) or beta.shape != (B, S, Hv):
+        raise ValueError("g and beta must be [B,S,Hv]")
+    if Hv % Hk != 0:
+        raise ValueError(f"Hv must be a multiple of Hk, got Hk={Hk} Hv={Hv}")
+    return B, S, Hk, Hv
+
+
+def _scratch_for(device, nbytes):
+    key = (device.type, device.index)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def _forward(q, k, v, g, beta, output_final_state, initial_state, path):
+    q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+    B, S, Hk, Hv = _check_inputs(q, k, v, g, beta)
+    if not q.is_cuda:
+        raise RuntimeError("gdn_chunk needs CUDA tensors (sm_100a); there is no CPU path")
+    lib = _lib.load()
+    dev = q.device
+    for name, x in (("k", k), ("v", v), ("g", g), ("beta", beta)):
+        if x.device != dev:
+            raise ValueError(f"{name} is on {x.device}, q on {dev}")
+    q, k, v = (x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16) for x in (q, k, v))
+    if g.dtype == torch.bfloat16 and beta.dtype == torch.bfloat16:
+        gate = _lib.GATE_BF16
+    else:
+        g, beta = g.float(), beta.float()
+        gate = _lib.GATE_F32
+    h0 = None
+    if initial_state is not None:
+        if tuple(initial_state.shape) != (B, Hv, GDN_D, GDN_D):
+            raise ValueError(f"initial_state must be [B,Hv,{GDN_D},{GDN_D}], got {tuple(initial_state.shape)}")
+        h0 = initial_state.to(device=dev, dtype=torch.float32).contiguous()
+    out = torch.empty((B, S, Hv, GDN_D), dtype=torch.bfloat16, device=dev)
+    hT = torch.empty((B, Hv, GDN_D, GDN_D), dtype=torch.float32, device=dev) if output_final_state else None
+    code = _lib.PATHS[path]
+    with torch.cuda.device(dev):
+        nbytes = int(lib.gdn_chunk_scratch_bytes(B, S, Hk, Hv, code))
+        scratch = _scratch_for(dev, nbytes)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        st = lib.gdn_chunk_fwd_sm100(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+            h0.data_ptr() if h0 is not None else None, out.data_ptr(),
+            hT.data_ptr() if hT is not None else None, scratch.data_ptr(), scratch.numel(),
+            B, S, Hk, Hv, gate, code, stream)
+        _lib.check(st, "gdn_chunk_fwd_sm100")
+        if os.environ.get("GDN_CHUNK_CHECK_STATUS", "0") == "1":
+            check_device_status(dev)
+    return out, hT
+
+
+def check_device_status(device=None):
+    """Synchronise and raise if the last kernel on `device` reported a bounded wait that ran out."""
+    import ctypes
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    buf = _scratch.get((device.type, device.index))
+    if buf is None:
+        return
+    word = ctypes.c_int(0)
+    with torch.cuda.device(device):
+        st = _lib.load().gdn_chunk_read_status(buf.data_ptr(), torch.cuda.current_stream(device).cuda_stream,
+                                               ctypes.byref(word))
+    if st != _lib.GDN_OK:
+        raise _lib.GdnLibraryError(f"device status 0x{word.value:x}: {_lib.error_string(st)}")
+
+
+def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, path="auto"):
+    """GDN forward (chunked gated delta rule).
+
+    Args:
+        q, k: [B, S, Hk, D] bf16 - QK heads.
+        v:    [B, S, Hv, D] bf16 - V heads (Hv must be a multiple of Hk).
+        g, beta: [B, S, Hv] bf16 or fp32 - log-decay (<= 0) and update gate.
+        output_final_state: whether to return the final state.
+        initial_state: optional [B, Hv, D, D] state to start from (zeros when None).
+        path: "auto", or one of "simt", "fused_nv64", "fused_nv32" to force a kernel.
+
+    Returns:
+        out [B, S, Hv, D] bf16, and final_state [B, Hv, D, D] fp32 (None when not requested).
+    """
+    return _forward(q, k, v, g, beta, output_final_state, initial_state, path)
+
+
+def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt_eps=1e-2):
+    """Kept for call-site compatibility with the reference (gdn_chunk_interface.py:53-62).
+
+    The reference's two-level entry chooses between an approximate "reset" fast path and an exact
+    scan using eps / frac / gt_eps; this implementation is always exact, so those arguments are
+    accepted and ignored.  Returns (out, final_state, info) like the reference; info is an empty
+    fp32 tensor.
+    """
+    out, hT = _forward(q, k, v, g, beta, True, None, "auto")
+    return out, hT, torch.empty(0, dtype=torch.float32, device=out.device)
+
+
+def gdn_chunk_reference(q, k, v, g, beta, chunk_size=64, mode="chunk"):
+    """Pure-torch definition of the operator, for callers that want the correctness anchor the
+    reference exposes under this name (gdn_chunk_interface.py:65-72).  Runs on the inputs'
+    device in fp32; q/k must already be expanded to Hv heads, as in the reference."""
+    from .torch_definition import chunk_gated_delta_rule, recurrent_gated_delta_rule
+    if mode == "chunk":
+        return chunk_gated_delta_rule(q, k, v, g, beta, chunk_size=chunk_size, output_final_state=True)
+    return recurrent_gated_delta_rule(q, k, v, g, beta, output_final_state=True)

@@ -1,0 +1,103 @@
+/*
+ * C ABI of the sm_100a gdn_chunk forward library (libgdn_chunk_sm100.so).
+ *
+ * This is the boundary a host binding talks to: plain pointers and sizes, no torch types.
+ * Every pointer is a DEVICE pointer in the current CUDA context unless stated otherwise.
+ * The library allocates no device memory, never synchronises the stream (except the two
+ * diagnostic calls marked "synchronises") and never throws: every call returns a status.
+ *
+ * Each entry point names the interface of the reference project it stands in for
+ * (paths are relative to the reference project's root).
+ */
+#ifndef GDN_CHUNK_SM100_H
+#define GDN_CHUNK_SM100_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes returned by every call. */
+#define GDN_OK 0
+#define GDN_ERR_BAD_ARGUMENT 1   /* shape, alignment, dtype or path value not accepted            */
+#define GDN_ERR_SCRATCH 2        /* scratch pointer missing, misaligned or smaller than required  */
+#define GDN_ERR_CUDA 3           /* a CUDA runtime call or a kernel launch failed                  */
+#define GDN_ERR_DRIVER 4         /* the driver rejected a TMA tensor-map description               */
+#define GDN_ERR_DEVICE 5         /* a kernel reported a bounded wait that ran out (see read_status) */
+
+/* dtype of g and beta */
+#define GDN_GATE_BF16 0
+#define GDN_GATE_F32 1
+
+/* execution path */
+#define GDN_PATH_AUTO 0          /* the fused tcgen05 kernel, column split chosen from B*Hv          */
+#define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
+#define GDN_PATH_FUSED_NV64 2    /* fused tcgen05 kernel, 64 value columns per CTA                  */
+#define GDN_PATH_FUSED_NV32 3    /* fused tcgen05 kernel, 32 value columns per CTA                  */
+
+#define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
+#define GDN_CHUNK 64             /* tokens per chunk                                                */
+
+/*
+ * Bytes of scratch gdn_chunk_fwd_sm100 needs for a problem.  256-byte aligned device memory,
+ * owned by the caller, reusable across calls on the same stream.
+ * Stands in for the workspace tensors the reference allocates inside its host wrapper
+ * (csrc/gdn_chunk/gdn_ops.cu:324-336, :812-813).
+ */
+size_t gdn_chunk_scratch_bytes(int B, int S, int Hq, int Hv, int path);
+
+/*
+ * Forward pass of the chunked gated delta rule.
+ *
+ *   q, k   [B,S,Hq,128] bf16        v   [B,S,Hv,128] bf16        g, beta [B,S,Hv] bf16 or fp32
+ *   h0     [B,Hv,128,128] fp32 (Dk rows, Dv columns) or NULL for a zero initial state
+ *   out    [B,S,Hv,128] bf16        hT  [B,Hv,128,128] fp32 or NULL when the final state is not wanted
+ *
+ * g is the log decay (<= 0), beta the update gate; q is scaled by 128^-0.5 inside; v-head h reads
+ * qk-head h / (Hv/Hq).  S need not be a multiple of 64.  All tensors contiguous, 16-byte aligned.
+ * Launches on `stream` (a cudaStream_t) of the current device and returns without waiting.
+ *
+ * Replaces the production entry of the reference's extension, forward_gdn_chunk_auto
+ * (csrc/gdn_chunk/gdn_ops.cu:969-1017), and the launchers beneath it: gdn_chunk_forward
+ * (csrc/gdn_chunk/gdn_kernel.cu:2855), gdn_chunk_replay_fused (gdn_kernel.cu:2929-2961) and the
+ * scan stages (csrc/gdn_chunk/gdn_scan_stage1.cu:562, gdn_scan_stage2.cu:228).  Extends them with
+ * an initial state and an fp32 final state, as the reference's torch definition has
+ * (gdn_qsa_sm80/reference/gdn_chunk_ref.py:20-31).
+ */
+int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                        const float* h0, void* out, float* hT, void* scratch, size_t scratch_bytes,
+                        int B, int S, int Hq, int Hv, int gate_dtype, int path, void* stream);
+
+/*
+ * Synchronises `stream`, then copies the device status word kept at the start of `scratch` into
+ * *device_status (0 = no kernel reported a problem).  Returns GDN_ERR_DEVICE when it is non-zero.
+ * Counterpart of C10_CUDA_KERNEL_LAUNCH_CHECK after the reference's launches
+ * (csrc/gdn_chunk/gdn_ops.cu:382, :862).
+ */
+int gdn_chunk_read_status(const void* scratch, void* stream, int* device_status);
+
+/* Static description of a status code (host pointer, never NULL). */
+const char* gdn_chunk_error_string(int status);
+
+/* Number of kernels this library has launched in this process so far (all devices). */
+unsigned long long gdn_chunk_kernel_launches(void);
+
+/*
+ * Diagnostic: one UMMA (tcgen05.mma) product with operands laid out by the library's own
+ * shared-memory layout helpers, for checking descriptors in isolation.  Synchronises.
+ *
+ *   a_rowmajor [M][K] bf16, b_rowmajor [N][K] bf16 (device) ; d_out [128][N] fp32 (device):
+ *   TMEM lanes 0..127 as read back, so an M = 64 product shows where its rows live.
+ *   a_major / b_major: 0 = K-major (128-byte swizzled rows), 1 = MN-major;
+ *   b_span: bytes per row of the MN-major B tile (128 or 64); use_tma != 0 stages the tiles
+ *   with TMA instead of thread stores.
+ * No counterpart in the reference (it unit-tests layouts by hand, csrc/gdn_chunk/gdn_scan_stage1.cu:238-245).
+ */
+int gdn_umma_probe(const void* a_rowmajor, const void* b_rowmajor, float* d_out, int* status_word,
+                   int M, int N, int K, int a_major, int b_major, int b_span, int use_tma, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GDN_CHUNK_SM100_H */
