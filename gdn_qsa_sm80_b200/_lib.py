@@ -35,6 +35,7 @@ EXPORTS = (
     "gdn_chunk_read_status",
     "gdn_chunk_error_string",
     "gdn_chunk_kernel_launches",
+    "gdn_chunk_set_phase_profile",
     "gdn_umma_probe",
 )
 
@@ -67,6 +68,8 @@ def load() -> ctypes.CDLL:
     lib.gdn_chunk_error_string.restype = ctypes.c_char_p
     lib.gdn_chunk_kernel_launches.argtypes = []
     lib.gdn_chunk_kernel_launches.restype = ctypes.c_ulonglong
+    lib.gdn_chunk_set_phase_profile.argtypes = [vp]
+    lib.gdn_chunk_set_phase_profile.restype = None
     lib.gdn_umma_probe.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp]
     lib.gdn_umma_probe.restype = ci
     _lib = lib

@@ -51,6 +51,8 @@ int encode_tma_bf16(void* tmap_out, const void* base, int rank, const unsigned l
     return r == CUDA_SUCCESS ? 0 : 1;
 }
 
+static long long* g_phase_profile = nullptr;
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace gdn
@@ -98,6 +100,7 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
     p.out = static_cast<__nv_bfloat16*>(out);
     p.hT = hT;
     p.status = static_cast<int*>(scratch);
+    p.prof = g_phase_profile;
     p.B = B; p.S = S; p.Hq = Hq; p.Hv = Hv;
     p.gate_f32 = gate_dtype == GDN_GATE_F32;
 
@@ -130,6 +133,8 @@ const char* gdn_chunk_error_string(int status) {
         default: return "unknown status";
     }
 }
+
+void gdn_chunk_set_phase_profile(void* device_buffer) { g_phase_profile = static_cast<long long*>(device_buffer); }
 
 unsigned long long gdn_chunk_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -62,6 +62,7 @@ constexpr uint32_t kColQS = 256;   // NV : Q S (lanes 0-63) / W S (lanes 64-127)
 constexpr uint32_t kColPV = 320;   // NV : P v_new (lanes 0-63)
 constexpr uint32_t kColKV = 384;   // NV : K^T v~ (all lanes)
 constexpr uint32_t kTmemCols = 512;
+constexpr int kProfSlots = 16;
 
 template <int NV>
 __device__ __forceinline__ void store_row_bf16(uint8_t* tile, uint32_t row, const float* x) {
@@ -97,6 +98,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     __shared__ float gam_s[kChunk];     // gamma * log2(e)
     __shared__ float bet_s[kChunk];
     __shared__ float wsum_s[2];
+    __shared__ long long prof_s[kProfSlots];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
@@ -141,6 +143,20 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
     uint32_t ph_tma = 0, ph_mma = 0;
     bool ok = true;
+
+    // optional per-phase cycle accounting by one thread of CTA (0,0,0)
+    const bool prof_on = p.prof != nullptr && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    long long prof_t = 0;
+    if (prof_on) {
+        for (int i = 0; i < kProfSlots; ++i) prof_s[i] = 0;
+        prof_t = clock64();
+    }
+#define GDN_PHASE(n)                                   \
+    if (prof_on) {                                     \
+        const long long now_ = clock64();              \
+        prof_s[n] += now_ - prof_t;                    \
+        prof_t = now_;                                 \
+    }
 
     for (int t = 0; t < NT && ok; ++t) {
         const int s0 = t * kChunk;
@@ -188,6 +204,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         ok = __syncthreads_and(ok);
         if (!ok) break;
 
+        GDN_PHASE(0)
         // ---- D1 = [K;Q] K^T --------------------------------------------------------------------------
         if (tid == 0) {
             tc_fence_after_sync();
@@ -206,6 +223,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (!ok) break;
         tc_fence_after_sync();
 
+        GDN_PHASE(1)
         // ---- mask epilogue: A (fp32, for the solve) and P (bf16 operand) -----------------------------
         {
             const int i = tid & 63;
@@ -257,6 +275,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tc_fence_before_sync();
         __syncthreads();
 
+        GDN_PHASE(2)
         // ---- T = (I + A)^-1, blocked: 16x16 diagonal blocks by substitution, then two merge levels ----
         if (tid < 64) {
             const int blk = tid >> 4, c = tid & 15;
@@ -275,6 +294,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             for (int i = 0; i < 16; ++i) Tm[(16 * blk + i) * kAsStride + 16 * blk + c] = x[i];
         }
         __syncthreads();
+        GDN_PHASE(3)
         {   // level 1: within each 32x32 diagonal block, X21 = -X22 (A21 X11)
             const int pr = tid >> 6, i = (tid >> 2) & 15, c0 = (tid & 3) * 4;
             const float* a21 = As + (32 * pr + 16 + i) * kAsStride + 32 * pr;
@@ -302,6 +322,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 make_float4(-z[0], -z[1], -z[2], -z[3]);
         }
         __syncthreads();
+        GDN_PHASE(4)
         {   // level 2: X[32:64, 0:32] = -T[32:64,32:64] (A[32:64,0:32] T[0:32,0:32])
             const int i = tid >> 2, c0 = (tid & 3) * 8;
             const float* all = As + (32 + i) * kAsStride;
@@ -339,6 +360,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             *reinterpret_cast<float4*>(Tm + (32 + i) * kAsStride + c0 + 4) = make_float4(-z[4], -z[5], -z[6], -z[7]);
         }
         __syncthreads();
+        GDN_PHASE(5)
         {   // T' = T diag(beta e^gamma) (rows 0-63), T'' = T diag(beta) (rows 64-127), bf16, K-major operand
             const int i = tid & 63, which = tid >> 6;
 #pragma unroll
@@ -363,6 +385,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         fence_proxy_async_smem();
         __syncthreads();
 
+        GDN_PHASE(6)
         // ---- D2 = [T';T''] [K | V] -------------------------------------------------------------------
         if (tid == 0) {
             tc_fence_after_sync();
@@ -388,6 +411,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (!ok) break;
         tc_fence_after_sync();
 
+        GDN_PHASE(7)
         // ---- W: TMEM fp32 -> bf16 rows 64-127 of the [Q;W] operand ----------------------------------
         if (warp < 2) {
             uint32_t r[32];
@@ -411,6 +435,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tc_fence_before_sync();
         __syncthreads();
 
+        GDN_PHASE(8)
         // ---- D3 = [Q;W] S ----------------------------------------------------------------------------
         if (tid == 0) {
             tc_fence_after_sync();
@@ -429,6 +454,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (!ok) break;
         tc_fence_after_sync();
 
+        GDN_PHASE(9)
         // ---- v_new = U - W S (token rows on lanes 64-127) ---------------------------------------------
         if (warp >= 2) {
             const int i = tid - 64;
@@ -454,6 +480,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tc_fence_before_sync();
         __syncthreads();
 
+        GDN_PHASE(10)
         // ---- D4 = P v_new ; D5 = K^T v~ ----------------------------------------------------------------
         if (tid == 0) {
             tc_fence_after_sync();
@@ -479,6 +506,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (!ok) break;
         tc_fence_after_sync();
 
+        GDN_PHASE(11)
         // ---- O rows (lanes 0-63) ------------------------------------------------------------------------
         if (warp < 2) {
             const int i = tid, s = s0 + i;
@@ -521,7 +549,11 @@ gdn_chunk_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
+        GDN_PHASE(12)
     }
+#undef GDN_PHASE
+    if (prof_on)
+        for (int i = 0; i < kProfSlots; ++i) p.prof[i] = prof_s[i];
 
     if (ok && p.hT) {
 #pragma unroll

@@ -23,6 +23,7 @@ struct Problem {
     __nv_bfloat16* out;
     float* hT;             // may be null
     int* status;           // device status word (never null)
+    long long* prof;       // optional: 16 per-phase cycle counters written by CTA (0,0,0); null = off
     int B, S, Hq, Hv;
     int gate_f32;          // 0: g/beta are bf16, 1: fp32
 };

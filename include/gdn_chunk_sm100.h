@@ -84,6 +84,15 @@ const char* gdn_chunk_error_string(int status);
 unsigned long long gdn_chunk_kernel_launches(void);
 
 /*
+ * Diagnostic: when `device_buffer` (16 x int64, device memory) is not NULL, CTA (0,0,0) of every
+ * later fused-kernel launch writes the SM clock cycles one of its threads spent in each phase of the
+ * chunk loop, summed over chunks.  NULL switches it off.  Process-wide, not thread-safe.
+ * Plays the role of the temporary clock64() instrumentation the reference's authors describe
+ * (docs/VALIDATION_LOG.md:108-109).
+ */
+void gdn_chunk_set_phase_profile(void* device_buffer);
+
+/*
  * Diagnostic: one UMMA (tcgen05.mma) product with operands laid out by the library's own
  * shared-memory layout helpers, for checking descriptors in isolation.  Synchronises.
  *
