@@ -26,11 +26,15 @@ PATH_AUTO = 0
 PATH_SIMT = 1
 PATH_FUSED_NV64 = 2
 PATH_FUSED_NV32 = 3
-PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "fused_nv64": PATH_FUSED_NV64, "fused_nv32": PATH_FUSED_NV32}
+PATH_TWOPASS_NV64 = 4
+PATH_TWOPASS_NV32 = 5
+PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "fused_nv64": PATH_FUSED_NV64, "fused_nv32": PATH_FUSED_NV32,
+         "twopass_nv64": PATH_TWOPASS_NV64, "twopass_nv32": PATH_TWOPASS_NV32}
 
 # Every symbol the public header declares (checked by the CPU tests).
 EXPORTS = (
     "gdn_chunk_scratch_bytes",
+    "gdn_chunk_workspace_offsets",
     "gdn_chunk_fwd_sm100",
     "gdn_chunk_read_status",
     "gdn_chunk_error_string",
@@ -60,6 +64,8 @@ def load() -> ctypes.CDLL:
     vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
     lib.gdn_chunk_scratch_bytes.argtypes = [ci, ci, ci, ci, ci]
     lib.gdn_chunk_scratch_bytes.restype = sz
+    lib.gdn_chunk_workspace_offsets.argtypes = [ci, ci, ci, ci, ctypes.POINTER(sz)]
+    lib.gdn_chunk_workspace_offsets.restype = ci
     lib.gdn_chunk_fwd_sm100.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, vp]
     lib.gdn_chunk_fwd_sm100.restype = ci
     lib.gdn_chunk_read_status.argtypes = [vp, vp, ctypes.POINTER(ci)]

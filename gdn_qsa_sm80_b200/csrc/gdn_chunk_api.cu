@@ -30,8 +30,8 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-int encode_tma_bf16(void* tmap_out, const void* base, int rank, const unsigned long long* dims,
-                    const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes) {
+int encode_tma(void* tmap_out, const void* base, int elem_bytes, int rank, const unsigned long long* dims,
+               const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return 1;
     cuuint64_t gdim[5], gstr[4];
@@ -45,10 +45,28 @@ int encode_tma_bf16(void* tmap_out, const void* base, int rank, const unsigned l
     const CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                   : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                                                         : CU_TENSOR_MAP_SWIZZLE_NONE;
-    const CUresult r = fn(static_cast<CUtensorMap*>(tmap_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
+    const CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUresult r = fn(static_cast<CUtensorMap*>(tmap_out), dt, rank,
                           const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : 1;
+}
+
+int encode_qkv_maps(const Problem& p, void* tq, void* tk, void* tv, int v_box_cols) {
+    const unsigned long long dq[4] = {static_cast<unsigned long long>(kD), static_cast<unsigned long long>(p.Hq),
+                                      static_cast<unsigned long long>(p.S), static_cast<unsigned long long>(p.B)};
+    const unsigned long long sq[3] = {kD * 2ull, static_cast<unsigned long long>(p.Hq) * kD * 2ull,
+                                      static_cast<unsigned long long>(p.S) * p.Hq * kD * 2ull};
+    const unsigned long long dv[4] = {static_cast<unsigned long long>(kD), static_cast<unsigned long long>(p.Hv),
+                                      static_cast<unsigned long long>(p.S), static_cast<unsigned long long>(p.B)};
+    const unsigned long long sv[3] = {kD * 2ull, static_cast<unsigned long long>(p.Hv) * kD * 2ull,
+                                      static_cast<unsigned long long>(p.S) * p.Hv * kD * 2ull};
+    const unsigned box_qk[4] = {64, 1, 64, 1};
+    const unsigned box_v[4] = {static_cast<unsigned>(v_box_cols), 1, 64, 1};
+    if (encode_tma(tq, p.q, 2, 4, dq, sq, box_qk, 128)) return 1;
+    if (encode_tma(tk, p.k, 2, 4, dq, sq, box_qk, 128)) return 1;
+    if (encode_tma(tv, p.v, 2, 4, dv, sv, box_v, v_box_cols * 2)) return 1;
+    return 0;
 }
 
 static long long* g_phase_profile = nullptr;
@@ -61,9 +79,27 @@ using namespace gdn;
 
 extern "C" {
 
+static size_t tiles_of(int B, int S, int Hv) {
+    return static_cast<size_t>(B) * Hv * ((S + kChunk - 1) / kChunk);
+}
+
+static bool path_uses_workspace(int path) {
+    return path == GDN_PATH_AUTO || path == GDN_PATH_TWOPASS_NV64 || path == GDN_PATH_TWOPASS_NV32;
+}
+
 size_t gdn_chunk_scratch_bytes(int B, int S, int Hq, int Hv, int path) {
-    (void)B; (void)S; (void)Hq; (void)Hv; (void)path;
-    return 256;   // the device status word, padded
+    (void)Hq;
+    if (B <= 0 || S < 0 || Hv <= 0) return 0;
+    if (!path_uses_workspace(path)) return 256;   // only the device status word, padded
+    return workspace_layout(tiles_of(B, S, Hv)).total;
+}
+
+int gdn_chunk_workspace_offsets(int B, int S, int Hq, int Hv, size_t* offsets) {
+    (void)Hq;
+    if (B <= 0 || S < 0 || Hv <= 0 || !offsets) return GDN_ERR_BAD_ARGUMENT;
+    const WorkspaceLayout l = workspace_layout(tiles_of(B, S, Hv));
+    offsets[0] = l.W; offsets[1] = l.P; offsets[2] = l.U; offsets[3] = l.vec; offsets[4] = l.total;
+    return GDN_OK;
 }
 
 int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
@@ -72,7 +108,7 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
-    if (path < GDN_PATH_AUTO || path > GDN_PATH_FUSED_NV32) return GDN_ERR_BAD_ARGUMENT;
+    if (path < GDN_PATH_AUTO || path > GDN_PATH_TWOPASS_NV32) return GDN_ERR_BAD_ARGUMENT;
     if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u) ||
         scratch_bytes < gdn_chunk_scratch_bytes(B, S, Hq, Hv, path))
         return GDN_ERR_SCRATCH;
@@ -105,11 +141,23 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
     p.gate_f32 = gate_dtype == GDN_GATE_F32;
 
     if (path == GDN_PATH_SIMT) return launch_simt(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
+    if (path == GDN_PATH_FUSED_NV64) return launch_fused(p, 64, stream);
+    if (path == GDN_PATH_FUSED_NV32) return launch_fused(p, 32, stream);
+    // two-kernel path: "prepare" over all chunks in parallel, then the serial "chain"
     int nv;
-    if (path == GDN_PATH_FUSED_NV64) nv = 64;
-    else if (path == GDN_PATH_FUSED_NV32) nv = 32;
-    else nv = (static_cast<long long>(B) * Hv * 2 >= 148) ? 64 : 32;   // fill the 148 SMs when B*Hv is small
-    return launch_fused(p, nv, stream);
+    if (path == GDN_PATH_TWOPASS_NV64) nv = 64;
+    else if (path == GDN_PATH_TWOPASS_NV32) nv = 32;
+    else nv = (static_cast<long long>(B) * Hv * 2 >= 148) ? 64 : 32;   // enough CTAs for the 148 SMs when B*Hv is small
+    const WorkspaceLayout l = workspace_layout(tiles_of(B, S, Hv));
+    uint8_t* base = static_cast<uint8_t*>(scratch);
+    Workspace ws;
+    ws.W = reinterpret_cast<__nv_bfloat16*>(base + l.W);
+    ws.P = reinterpret_cast<__nv_bfloat16*>(base + l.P);
+    ws.U = reinterpret_cast<float*>(base + l.U);
+    ws.vec = reinterpret_cast<float*>(base + l.vec);
+    const int st = launch_prepare(p, ws, stream);
+    if (st != GDN_OK) return st;
+    return launch_chain(p, ws, nv, stream);
 }
 
 int gdn_chunk_read_status(const void* scratch, void* stream_, int* device_status) {

@@ -1,0 +1,240 @@
+// "prepare": everything of a chunk that does not depend on the recurrent state, one CTA per
+// (batch, value head, chunk), fully parallel over the sequence.
+//
+// For each 64-token chunk it produces, in the notation of the reference's torch definition
+// (gdn_qsa_sm80/reference/gdn_chunk_ref.py:56-78):
+//   gamma   inclusive cumsum of the log gate (warp shuffles), and from it the per-token factors
+//           exp(gamma_C - gamma_i), scale*exp(gamma_i), exp(gamma_C)                  -> vec  [256] fp32
+//   P     = tril(scale * exp(gamma_i - gamma_j) * Q K^T)          ("intra_chunk_attn")  -> P    [64][64]  bf16
+//   T     = (I + tril(beta_i exp(gamma_i - gamma_j) K K^T, -1))^-1
+//   W     = T (beta e^gamma K)                                   ("k_cumdecay")        -> W    [64][128] bf16
+//   U     = T (beta V)                                           ("new_values")        -> U    [64][128] fp32
+// K K^T, Q K^T, T [beta e^gamma K | beta V] run on tcgen05 with TMA-staged tiles; the decay mask is
+// applied in fp32 while the raw products move from TMEM to registers.  The reference computes the
+// same quantities in gdn_prepare_kernel (csrc/gdn_chunk/gdn_kernel.cu:343-710) at chunk 16 with the
+// decay folded into the operands; here the pairwise factor exp(gamma_i - gamma_j) <= 1 is used, which
+// stays finite at chunk 64.
+//
+// 106 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and one CTA's
+// tensor-core and TMA latencies hide behind the other's CUDA-core phases.
+#include <cuda.h>
+
+#include "../../include/gdn_chunk_sm100.h"
+#include "gdn_common.cuh"
+#include "gdn_prep_device.cuh"
+#include "ptx_sm100.cuh"
+
+namespace gdn {
+namespace {
+
+struct PSmem {
+    static constexpr uint32_t KQ = 0;                    // [K;Q]: 2 k-halves x 128 rows x 128 B
+    static constexpr uint32_t VT = KQ + 32768;           // V: 2 column halves x 64 rows x 128 B
+    static constexpr uint32_t TS = VT + 16384;           // [T';T'']: 128 rows x 128 B
+    static constexpr uint32_t AS = TS + 16384;           // A fp32 64 x 68
+    static constexpr uint32_t TM = AS + 17408;           // T fp32 64 x 68
+    static constexpr uint32_t YT = TM + 17408;           // merge temporaries
+    static constexpr uint32_t kBytes = YT + 5120;
+    static constexpr uint32_t kDynamic = kBytes + 1024;
+};
+constexpr uint32_t kPrepTmemCols = 256;   // W | U; the raw K K^T / Q K^T accumulator reuses the first 64 columns
+
+template <bool GATE_F32>
+__global__ void __launch_bounds__(128, 2)
+gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, Problem p, Workspace ws) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t sm_u32 = smem_u32(sm);
+    __shared__ __align__(8) uint64_t bar_tma;
+    __shared__ __align__(8) uint64_t bar_mma;
+    __shared__ uint32_t tmem_slot;
+    __shared__ __align__(16) PrepScratch ps;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int t = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
+    const int hq = hv / (p.Hv / p.Hq);
+    const int NT = gridDim.x;
+    const int s0 = t * kChunk;
+    const size_t tile = (static_cast<size_t>(b) * p.Hv + hv) * NT + t;
+    const float scale = rsqrtf(static_cast<float>(kD));
+
+    if (tid == 0) {
+        mbar_init(&bar_tma, 1);
+        mbar_init(&bar_mma, 1);
+        fence_mbar_init();
+        mbar_arrive_expect_tx(&bar_tma, 6 * 8192);
+        tma_load_4d(sm + PSmem::KQ + 0, &tm_k, &bar_tma, 0, hq, s0, b);        // K, d 0-63   -> rows 0-63
+        tma_load_4d(sm + PSmem::KQ + 16384, &tm_k, &bar_tma, 64, hq, s0, b);   // K, d 64-127
+        tma_load_4d(sm + PSmem::KQ + 8192, &tm_q, &bar_tma, 0, hq, s0, b);     // Q           -> rows 64-127
+        tma_load_4d(sm + PSmem::KQ + 24576, &tm_q, &bar_tma, 64, hq, s0, b);
+        tma_load_4d(sm + PSmem::VT + 0, &tm_v, &bar_tma, 0, hv, s0, b);        // V, dv 0-63
+        tma_load_4d(sm + PSmem::VT + 8192, &tm_v, &bar_tma, 64, hv, s0, b);    // V, dv 64-127
+    }
+    if (warp == 0) {
+        tmem_alloc(&tmem_slot, kPrepTmemCols);
+        tmem_relinquish();
+    }
+    float* As = reinterpret_cast<float*>(sm + PSmem::AS);
+    float* Tm = reinterpret_cast<float*>(sm + PSmem::TM);
+    float* Yt = reinterpret_cast<float*>(sm + PSmem::YT);
+    for (int e = tid; e < kChunk * kSolveStride; e += 128) Tm[e] = 0.f;
+
+    const int valid = min(kChunk, p.S - s0);
+    prep_gates<GATE_F32>(ps, p.g, p.beta, static_cast<size_t>(b) * p.S + s0, hv, p.Hv, valid, scale,
+                         ws.vec + tile * 256);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t lane_base = static_cast<uint32_t>(warp) * 32u;
+
+    bool ok = mbar_wait(&bar_tma, 0, p.status, kDevTimeoutTma);
+    ok = __syncthreads_and(ok);
+    uint32_t ph_mma = 0;
+
+    if (ok) {
+        if (tid == 0) {   // raw K K^T (lanes 0-63) and Q K^T (lanes 64-127)
+            tc_fence_after_sync();
+            constexpr uint32_t idesc = umma_idesc_bf16(128, 64, MAJOR_K, MAJOR_K);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint64_t ad = umma_smem_desc(sm_u32 + PSmem::KQ + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, SWZ_128B);
+                umma_bf16_ss(tmem, ad, ad, idesc, ks > 0);
+            }
+            umma_commit(&bar_mma);
+        }
+        ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
+        ph_mma ^= 1;
+        ok = __syncthreads_and(ok);
+    }
+    if (ok) {
+        tc_fence_after_sync();
+        const int i = tid & 63;
+        float ri, diag[16];
+        prep_row_setup(ps, i, ri, diag);
+        uint32_t r[32];
+        float f[32];
+        if (warp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
+            const float bi = ps.bet[i];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
+                prep_row_factors(ps, i, half, ri, diag, f);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    float4 o;
+                    o.x = (half * 32 + c + 0 < i) ? bi * f[c + 0] * __uint_as_float(r[c + 0]) : 0.f;
+                    o.y = (half * 32 + c + 1 < i) ? bi * f[c + 1] * __uint_as_float(r[c + 1]) : 0.f;
+                    o.z = (half * 32 + c + 2 < i) ? bi * f[c + 2] * __uint_as_float(r[c + 2]) : 0.f;
+                    o.w = (half * 32 + c + 3 < i) ? bi * f[c + 3] * __uint_as_float(r[c + 3]) : 0.f;
+                    *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
+                }
+            }
+        } else {          // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
+            __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
+                prep_row_factors(ps, i, half, ri, diag, f);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint4 pk;
+                    pk.x = pack_bf16x2(scale * f[8 * ch + 0] * __uint_as_float(r[8 * ch + 0]), scale * f[8 * ch + 1] * __uint_as_float(r[8 * ch + 1]));
+                    pk.y = pack_bf16x2(scale * f[8 * ch + 2] * __uint_as_float(r[8 * ch + 2]), scale * f[8 * ch + 3] * __uint_as_float(r[8 * ch + 3]));
+                    pk.z = pack_bf16x2(scale * f[8 * ch + 4] * __uint_as_float(r[8 * ch + 4]), scale * f[8 * ch + 5] * __uint_as_float(r[8 * ch + 5]));
+                    pk.w = pack_bf16x2(scale * f[8 * ch + 6] * __uint_as_float(r[8 * ch + 6]), scale * f[8 * ch + 7] * __uint_as_float(r[8 * ch + 7]));
+                    *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
+                }
+            }
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+
+        prep_invert_unit_lower(As, Tm, Yt);
+
+        {   // [T diag(beta e^gamma) ; T diag(beta)] as one 128-row K-major operand
+            const int which = tid >> 6;
+            prep_store_scaled_T_row(Tm, which == 0 ? ps.eg : ps.bet, i, sm + PSmem::TS, which * 64 + i);
+        }
+        fence_proxy_async_smem();
+        __syncthreads();
+
+        if (tid == 0) {   // W = T' K (lanes 0-63, columns 0-127), U = T'' V (lanes 64-127, columns 128-255)
+            tc_fence_after_sync();
+            constexpr uint32_t idesc = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_MN);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint64_t ad = umma_smem_desc(sm_u32 + PSmem::TS + ks * 32, 16, 1024, SWZ_128B);
+                const uint64_t bk = umma_smem_desc(sm_u32 + PSmem::KQ + ks * 2048, 16384, 1024, SWZ_128B);
+                umma_bf16_ss(tmem, ad, bk, idesc, ks > 0);
+            }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint64_t ad = umma_smem_desc(sm_u32 + PSmem::TS + ks * 32, 16, 1024, SWZ_128B);
+                const uint64_t bv = umma_smem_desc(sm_u32 + PSmem::VT + ks * 2048, 8192, 1024, SWZ_128B);
+                umma_bf16_ss(tmem + 128, ad, bv, idesc, ks > 0);
+            }
+            umma_commit(&bar_mma);
+        }
+        ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
+        ph_mma ^= 1;
+        ok = __syncthreads_and(ok);
+    }
+    if (ok) {
+        tc_fence_after_sync();
+        const int i = tid & 63;
+        uint32_t r[32];
+        if (warp < 2) {
+            __nv_bfloat16* wrow = ws.W + tile * (kChunk * kD) + static_cast<size_t>(i) * kD;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                tmem_ld_x32(tmem_addr(tmem, lane_base, q4 * 32), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint4 pk;
+                    pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                    pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                    pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                    pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                    *reinterpret_cast<uint4*>(wrow + q4 * 32 + 8 * ch) = pk;
+                }
+            }
+        } else {
+            float* urow = ws.U + tile * (kChunk * kD) + static_cast<size_t>(i) * kD;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                tmem_ld_x32(tmem_addr(tmem, lane_base, 128 + q4 * 32), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 32; c += 4)
+                    *reinterpret_cast<uint4*>(urow + q4 * 32 + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kPrepTmemCols);
+}
+
+}  // namespace
+
+int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream) {
+    alignas(64) CUtensorMap tq, tk, tv;
+    if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
+    const int NT = (p.S + kChunk - 1) / kChunk;
+    auto go = [&](auto kernel) -> int {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PSmem::kDynamic) != cudaSuccess)
+            return GDN_ERR_CUDA;
+        const dim3 grid(NT, p.Hv, p.B), block(128);
+        kernel<<<grid, block, PSmem::kDynamic, stream>>>(tq, tk, tv, p, ws);
+        count_launch();
+        return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
+    };
+    return p.gate_f32 ? go(gdn_prepare_kernel<true>) : go(gdn_prepare_kernel<false>);
+}
+
+}  // namespace gdn

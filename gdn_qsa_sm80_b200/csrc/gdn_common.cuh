@@ -28,6 +28,29 @@ struct Problem {
     int gate_f32;          // 0: g/beta are bf16, 1: fp32
 };
 
+// Workspace of the two-kernel path (device pointers into the caller's scratch buffer).
+// One tile per (batch, value head, chunk): tile = (b * Hv + hv) * NT + t.
+struct Workspace {
+    __nv_bfloat16* W;   // [tiles][64][128]  W = T (beta e^gamma K)
+    __nv_bfloat16* P;   // [tiles][64][64]   masked, scaled Q K^T
+    float* U;           // [tiles][64][128]  U = T (beta V)
+    float* vec;         // [tiles][256]      exp(gamma_C-gamma_i) | scale exp(gamma_i) | exp(gamma_C) | pad
+};
+
+// Byte offsets of the workspace arrays inside the scratch buffer (the status word sits at offset 0).
+struct WorkspaceLayout {
+    size_t W, P, U, vec, total;
+};
+inline WorkspaceLayout workspace_layout(size_t tiles) {
+    WorkspaceLayout l;
+    l.W = 1024;
+    l.P = l.W + tiles * 16384;
+    l.U = l.P + tiles * 8192;
+    l.vec = l.U + tiles * 32768;
+    l.total = l.vec + tiles * 1024;
+    return l;
+}
+
 // Device status codes written by kernels (0 = fine).  The low byte says which wait gave up.
 constexpr int kDevTimeoutTma = 0x101;
 constexpr int kDevTimeoutMma = 0x102;
@@ -40,10 +63,21 @@ cudaError_t launch_simt(const Problem& p, cudaStream_t stream);
 // Fused tcgen05 kernel; nv = value columns per CTA (32 or 64).  Returns a GDN_* status.
 int launch_fused(const Problem& p, int nv, cudaStream_t stream);
 
-// Host helper: encode a tiled TMA descriptor for a row-major bf16 tensor of `rank` dims
+// "prepare" (state-independent per-chunk quantities into the workspace) and "chain" (the serial
+// state recurrence plus outputs, reading the workspace).  Both return a GDN_* status.
+int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream);
+int launch_chain(const Problem& p, const Workspace& ws, int nv, cudaStream_t stream);
+
+// Host helper: encode a tiled TMA descriptor for a row-major tensor of `rank` dims
 // (dims/strides innermost first; strides in bytes for dims 1..rank-1).  swizzle_bytes: 128 or 64.
-// Returns 0 on success.
-int encode_tma_bf16(void* tmap_out, const void* base, int rank, const unsigned long long* dims,
-                    const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes);
+// elem_bytes: 2 = bf16, 4 = fp32.  Returns 0 on success.
+int encode_tma(void* tmap_out, const void* base, int elem_bytes, int rank, const unsigned long long* dims,
+               const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes);
+inline int encode_tma_bf16(void* tmap_out, const void* base, int rank, const unsigned long long* dims,
+                           const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes) {
+    return encode_tma(tmap_out, base, 2, rank, dims, strides_bytes, box, swizzle_bytes);
+}
+// TMA descriptors of q, k ([B,S,Hq,128], 64x64 boxes) and v ([B,S,Hv,128], v_box_cols x 64 boxes).
+int encode_qkv_maps(const Problem& p, void* tq, void* tk, void* tv, int v_box_cols);
 
 }  // namespace gdn

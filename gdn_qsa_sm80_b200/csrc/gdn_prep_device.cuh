@@ -1,0 +1,261 @@
+// Device-side building blocks of the state-independent ("prepare") part of a chunk, shared by the
+// kernels that need it: gate cumsum and decay tables, the masked K K^T / Q K^T epilogue, and the
+// 64x64 unit-lower-triangular inverse T = (I + A)^-1.
+//
+// All functions are executed by the same 128 threads (4 warps) and communicate through the
+// PrepScratch block in shared memory; callers place __syncthreads() where the comments say so.
+#pragma once
+
+#include "gdn_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace gdn {
+
+constexpr int kSolveStride = 68;   // fp32 row stride of the 64x64 solve matrices: 16-byte aligned rows,
+                                   // and 68 = 4 (mod 32) spreads rows over banks for row-wise and fragment reads
+constexpr int kY1Stride = 20;      // row stride of the 16-column temporaries of merge level 1
+constexpr int kY2Stride = 36;      // row stride of the 32-column temporary of merge level 2
+
+struct PrepScratch {
+    float gam[kChunk];        // gamma_j * log2(e): inclusive cumsum of the log gate inside the chunk
+    float bet[kChunk];        // beta_j (0 for padding tokens)
+    float eg[kChunk];         // beta_j * exp(gamma_j)
+    float ctab[3][kChunk];    // ctab[I-1][j] = exp(gamma_{16 I} - gamma_j) for j < 16 I  (always <= 1)
+    float wsum[2];
+};
+
+template <bool GATE_F32>
+__device__ __forceinline__ float prep_load_gate(const void* p, size_t idx) {
+    if (GATE_F32) return static_cast<const float*>(p)[idx];
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+}
+
+// Gate cumsum over the chunk by warp shuffles (threads 0-63 hold one token each) and the decay tables.
+// Contains two __syncthreads(); a third one is needed before the tables are read.
+// If vec_out != nullptr, also writes the per-token factors a later kernel needs:
+//   vec_out[i] = exp(gamma_C - gamma_i), vec_out[64+i] = scale * exp(gamma_i), vec_out[128] = exp(gamma_C).
+template <bool GATE_F32>
+__device__ __forceinline__ void prep_gates(PrepScratch& ps, const void* g, const void* beta, size_t tok0, int hv,
+                                           int Hv, int valid, float scale, float* vec_out) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float gsum = 0.f, bv = 0.f;
+    if (tid < kChunk) {
+        float gv = 0.f;
+        if (tid < valid) {
+            const size_t idx = (tok0 + tid) * Hv + hv;
+            gv = prep_load_gate<GATE_F32>(g, idx);
+            bv = prep_load_gate<GATE_F32>(beta, idx);
+        }
+        gsum = gv;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float y = __shfl_up_sync(0xffffffffu, gsum, o);
+            if (lane >= o) gsum += y;
+        }
+        if (lane == 31) ps.wsum[warp] = gsum;
+    }
+    __syncthreads();
+    if (tid < kChunk) {
+        if (warp == 1) gsum += ps.wsum[0];
+        ps.gam[tid] = gsum * kLog2e;
+        ps.bet[tid] = bv;
+    }
+    __syncthreads();
+    if (tid < kChunk) {
+        const float gi = ps.gam[tid], gC = ps.gam[kChunk - 1];
+        const float e = exp2f(gi);
+        ps.eg[tid] = bv * e;
+        if (vec_out) {
+            vec_out[tid] = exp2f(gC - gi);
+            vec_out[kChunk + tid] = scale * e;
+            if (tid == 0) vec_out[2 * kChunk] = exp2f(gC);
+        }
+    }
+    if (tid < 96) {   // 16 + 32 + 48 table entries
+        const int I = tid < 16 ? 1 : (tid < 48 ? 2 : 3);
+        const int j = tid - (I == 1 ? 0 : (I == 2 ? 16 : 48));
+        ps.ctab[I - 1][j] = exp2f(ps.gam[16 * I] - ps.gam[j]);
+    }
+}
+
+// Pairwise decay factors of row i for the 32 columns [32*half, 32*half+32):
+//   f[c] = exp(gamma_i - gamma_j) for j <= i, 0 above the diagonal.
+// Off-diagonal 16-blocks use exp(gamma_i - gamma_ref) * exp(gamma_ref - gamma_j) with ref = first token
+// of row i's block (both factors <= 1, so nothing overflows); the diagonal block uses direct exponentials.
+__device__ __forceinline__ void prep_row_factors(const PrepScratch& ps, int i, int half, float ri,
+                                                 const float (&diag)[16], float (&f)[32]) {
+    const int I = i >> 4;
+    const float* ct = ps.ctab[I > 0 ? I - 1 : 0];
+#pragma unroll
+    for (int J2 = 0; J2 < 2; ++J2) {
+        const int J = half * 2 + J2;
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+            const float off = ri * ct[16 * J + jj];
+            f[16 * J2 + jj] = (J < I) ? off : ((J == I) ? diag[jj] : 0.f);
+        }
+    }
+}
+
+// Per-thread setup for prep_row_factors: ri and the 16 diagonal-block factors of row i.
+__device__ __forceinline__ void prep_row_setup(const PrepScratch& ps, int i, float& ri, float (&diag)[16]) {
+    const int I = i >> 4, ii = i & 15;
+    const float gi = ps.gam[i];
+    ri = exp2f(gi - ps.gam[16 * I]);
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) diag[jj] = (jj <= ii) ? exp2f(gi - ps.gam[16 * I + jj]) : 0.f;
+}
+
+__device__ __forceinline__ uint32_t f32_to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+// Warp-level 16x8x8 TF32 product with fp32 accumulation (legacy tensor path; used only for the
+// small merge products of the triangular inverse, about 1% of the chunk's arithmetic).
+__device__ __forceinline__ void mma_tf32_16x8x8(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// A fragment (16 rows x 8 k) of a row-major fp32 matrix with row stride `ld`.
+__device__ __forceinline__ void load_a_frag(uint32_t (&a)[4], const float* m, int ld, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    a[0] = f32_to_tf32(m[g * ld + t]);
+    a[1] = f32_to_tf32(m[(g + 8) * ld + t]);
+    a[2] = f32_to_tf32(m[g * ld + t + 4]);
+    a[3] = f32_to_tf32(m[(g + 8) * ld + t + 4]);
+}
+// B fragment (8 k x 8 n) of a row-major fp32 matrix B[k][n] with row stride `ld`.
+__device__ __forceinline__ void load_b_frag(uint32_t (&b)[2], const float* m, int ld, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    b[0] = f32_to_tf32(m[t * ld + g]);
+    b[1] = f32_to_tf32(m[(t + 4) * ld + g]);
+}
+// Store an accumulator fragment (16 x 8), optionally negated.
+__device__ __forceinline__ void store_c_frag(float* m, int ld, int lane, const float (&c)[4], float sign) {
+    const int g = lane >> 2, t = lane & 3;
+    *reinterpret_cast<float2*>(m + g * ld + 2 * t) = make_float2(sign * c[0], sign * c[1]);
+    *reinterpret_cast<float2*>(m + (g + 8) * ld + 2 * t) = make_float2(sign * c[2], sign * c[3]);
+}
+
+// T = (I + A)^-1 for the strictly lower-triangular 64x64 A in `As` (fp32, row stride kSolveStride).
+// Result in `Tm` (same layout; must be zero above the 16x16 diagonal blocks on entry - the caller zeroes it).
+// `Yt` is a scratch of at least 32*kY2Stride floats.  Blocked inversion:
+//   16x16 diagonal blocks by forward substitution in fp32 registers, then
+//   [[L11,0],[L21,L22]]^-1 = [[X11,0],[-X22 L21 X11, X22]] at block sizes 16 and 32 with TF32 warp MMAs.
+// Contains its own __syncthreads(); `As` and `Tm` must be complete before the call (one barrier before).
+__device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* Tm, float* Yt) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < 64) {
+        const int blk = tid >> 4, c = tid & 15;
+        const float* a = As + (16 * blk) * kSolveStride + 16 * blk;
+        float4 rowv[15][4];
+#pragma unroll
+        for (int i = 1; i < 16; ++i)
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (4 * q < i) rowv[i - 1][q] = *reinterpret_cast<const float4*>(a + i * kSolveStride + 4 * q);
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = (i == c) ? 1.f : 0.f;
+#pragma unroll
+        for (int i = 1; i < 16; ++i) {
+            float acc0 = x[i], acc1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < i; ++j) {
+                const float4 v4 = rowv[i - 1][j >> 2];
+                const float aij = (j & 3) == 0 ? v4.x : ((j & 3) == 1 ? v4.y : ((j & 3) == 2 ? v4.z : v4.w));
+                if (j & 1) acc1 = fmaf(-aij, x[j], acc1);
+                else acc0 = fmaf(-aij, x[j], acc0);
+            }
+            x[i] = acc0 + acc1;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) Tm[(16 * blk + i) * kSolveStride + 16 * blk + c] = x[i];
+    }
+    __syncthreads();
+    {   // level 1: pairs of 16-blocks.  warp -> (pair p, 8-column tile nt)
+        const int p = warp >> 1, nt = warp & 1;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t a[4], b[2];
+            load_a_frag(a, As + (32 * p + 16) * kSolveStride + 32 * p + 8 * ks, kSolveStride, lane);
+            load_b_frag(b, Tm + (32 * p + 8 * ks) * kSolveStride + 32 * p + 8 * nt, kSolveStride, lane);
+            mma_tf32_16x8x8(acc, a, b);
+        }
+        store_c_frag(Yt + (16 * p) * kY1Stride + 8 * nt, kY1Stride, lane, acc, 1.f);
+        __syncthreads();
+        float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t a[4], b[2];
+            load_a_frag(a, Tm + (32 * p + 16) * kSolveStride + 32 * p + 16 + 8 * ks, kSolveStride, lane);
+            load_b_frag(b, Yt + (16 * p + 8 * ks) * kY1Stride + 8 * nt, kY1Stride, lane);
+            mma_tf32_16x8x8(acc2, a, b);
+        }
+        store_c_frag(Tm + (32 * p + 16) * kSolveStride + 32 * p + 8 * nt, kSolveStride, lane, acc2, -1.f);
+    }
+    __syncthreads();
+    {   // level 2: the 32x32 lower-left block.  warp -> (16-row block rb, 16-column block cb)
+        const int rb = warp >> 1, cb = warp & 1;
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t a[4];
+            load_a_frag(a, As + (32 + 16 * rb) * kSolveStride + 8 * ks, kSolveStride, lane);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t b[2];
+                load_b_frag(b, Tm + (8 * ks) * kSolveStride + 16 * cb + 8 * nt, kSolveStride, lane);
+                mma_tf32_16x8x8(acc[nt], a, b);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+            store_c_frag(Yt + (16 * rb) * kY2Stride + 16 * cb + 8 * nt, kY2Stride, lane, acc[nt], 1.f);
+        __syncthreads();
+        float acc2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t a[4];
+            load_a_frag(a, Tm + (32 + 16 * rb) * kSolveStride + 32 + 8 * ks, kSolveStride, lane);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t b[2];
+                load_b_frag(b, Yt + (8 * ks) * kY2Stride + 16 * cb + 8 * nt, kY2Stride, lane);
+                mma_tf32_16x8x8(acc2[nt], a, b);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+            store_c_frag(Tm + (32 + 16 * rb) * kSolveStride + 16 * cb + 8 * nt, kSolveStride, lane, acc2[nt], -1.f);
+    }
+    __syncthreads();
+}
+
+// Row `i` of  T diag(f)  as bf16 into row `dst_row` of a 128-byte-swizzled K-major tile
+// (f = beta e^gamma gives the operand that produces W, f = beta the one that produces U).
+__device__ __forceinline__ void prep_store_scaled_T_row(const float* Tm, const float* f, int i, uint8_t* tile,
+                                                        uint32_t dst_row) {
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+        const float4 t0 = *reinterpret_cast<const float4*>(Tm + i * kSolveStride + ch * 8);
+        const float4 t1 = *reinterpret_cast<const float4*>(Tm + i * kSolveStride + ch * 8 + 4);
+        const float4 f0 = *reinterpret_cast<const float4*>(f + ch * 8);
+        const float4 f1 = *reinterpret_cast<const float4*>(f + ch * 8 + 4);
+        uint4 pk;
+        pk.x = pack_bf16x2(t0.x * f0.x, t0.y * f0.y);
+        pk.y = pack_bf16x2(t0.z * f0.z, t0.w * f0.w);
+        pk.z = pack_bf16x2(t1.x * f1.x, t1.y * f1.y);
+        pk.w = pack_bf16x2(t1.z * f1.z, t1.w * f1.w);
+        *reinterpret_cast<uint4*>(tile + swz_chunk_offset<128>(dst_row, ch)) = pk;
+    }
+}
+
+}  // namespace gdn

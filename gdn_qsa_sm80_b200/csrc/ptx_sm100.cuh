@@ -79,6 +79,41 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     }
 }
 
+// Same, for warp-specialised kernels: a CTA-wide abort flag in shared memory makes every later
+// wait of every role return at once after the first time-out, so the CTA drains quickly.
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, int* status, int code,
+                                                    volatile int* abort_flag) {
+    if (*abort_flag) return false;
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            atomicCAS(status, 0, code);
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+// Named barrier among `count` threads (count a multiple of 32); id 0 is __syncthreads().
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// 1-D bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16), completing on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // Proxy fences
 // ---------------------------------------------------------------------------------------------

@@ -31,10 +31,12 @@ extern "C" {
 #define GDN_GATE_F32 1
 
 /* execution path */
-#define GDN_PATH_AUTO 0          /* the fused tcgen05 kernel, column split chosen from B*Hv          */
+#define GDN_PATH_AUTO 0          /* prepare + chain kernels, column split chosen from B*Hv             */
 #define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
-#define GDN_PATH_FUSED_NV64 2    /* fused tcgen05 kernel, 64 value columns per CTA                  */
-#define GDN_PATH_FUSED_NV32 3    /* fused tcgen05 kernel, 32 value columns per CTA                  */
+#define GDN_PATH_FUSED_NV64 2    /* single fused tcgen05 kernel, 64 value columns per CTA            */
+#define GDN_PATH_FUSED_NV32 3    /* single fused tcgen05 kernel, 32 value columns per CTA            */
+#define GDN_PATH_TWOPASS_NV64 4  /* prepare kernel + chain kernel, 64 value columns per chain CTA    */
+#define GDN_PATH_TWOPASS_NV32 5  /* prepare kernel + chain kernel, 32 value columns per chain CTA    */
 
 #define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
 #define GDN_CHUNK 64             /* tokens per chunk                                                */
@@ -46,6 +48,15 @@ extern "C" {
  * (csrc/gdn_chunk/gdn_ops.cu:324-336, :812-813).
  */
 size_t gdn_chunk_scratch_bytes(int B, int S, int Hq, int Hv, int path);
+
+/*
+ * Byte offsets, inside the scratch buffer, of the per-chunk arrays the prepare kernel writes and the
+ * chain kernel reads (paths AUTO and TWOPASS_*): offsets[0] W bf16 [tiles][64][128], [1] P bf16
+ * [tiles][64][64], [2] U fp32 [tiles][64][128], [3] per-token factors fp32 [tiles][256], [4] total
+ * bytes; tile = (b*Hv + hv)*ceil(S/64) + chunk.  For stage-level tests of "prepare", which the
+ * reference exposes as prepare_workspace (csrc/gdn_chunk/gdn_ops.cu:1026-1030).
+ */
+int gdn_chunk_workspace_offsets(int B, int S, int Hq, int Hv, size_t* offsets);
 
 /*
  * Forward pass of the chunked gated delta rule.

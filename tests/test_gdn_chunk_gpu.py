@@ -19,7 +19,8 @@ from helpers import assert_close, golden, oracle_f32
 
 pytestmark = pytest.mark.gpu
 
-PATHS = ["simt", "fused_nv64", "fused_nv32"]
+PATHS = ["simt", "fused_nv64", "fused_nv32", "twopass_nv64", "twopass_nv32"]
+TENSOR_PATHS = PATHS[1:]
 
 
 def run(q, k, v, g, beta, h0=None, path="auto", final=True):
@@ -95,7 +96,7 @@ def test_cpu_small_workload_on_gpu_matches_stored_reference():
     assert_close(st, z["state_chunk"], "state", rel=2e-2, mabs=5e-2)
 
 
-@pytest.mark.parametrize("path", ["fused_nv64", "fused_nv32"])
+@pytest.mark.parametrize("path", TENSOR_PATHS)
 def test_head_ratio_expansion_is_bit_identical(path):
     """Hk = 2 with Hv = 4 must equal pre-expanded Hk = 4 input (tests/test_gdn_chunk.py:52-60)."""
     q, k, v, g, beta, _ = bf16_inputs(256, seed=9)
@@ -104,7 +105,7 @@ def test_head_ratio_expansion_is_bit_identical(path):
     assert np.array_equal(o1, o2) and np.array_equal(s1, s2)
 
 
-@pytest.mark.parametrize("path", ["fused_nv64", "fused_nv32"])
+@pytest.mark.parametrize("path", TENSOR_PATHS)
 def test_run_twice_is_deterministic(path):
     q, k, v, g, beta, h0 = bf16_inputs(320, seed=21, h0=True)
     o1, s1 = run(q, k, v, g, beta, h0, path)
@@ -139,7 +140,7 @@ def test_bf16_gates_and_no_final_state_and_noncontiguous_inputs():
 def test_paths_agree_on_a_batched_problem():
     q, k, v, g, beta, h0 = bf16_inputs(384, seed=55, B=3, Hq=2, Hv=4, h0=True)
     ref_o, ref_s = run(q, k, v, g, beta, h0, "simt")
-    for path in ("fused_nv64", "fused_nv32", "auto"):
+    for path in TENSOR_PATHS + ["auto"]:
         o, s = run(q, k, v, g, beta, h0, path)
         assert_close(o, ref_o, f"out[{path}] vs simt")
         assert_close(s, ref_s, f"state[{path}] vs simt")
