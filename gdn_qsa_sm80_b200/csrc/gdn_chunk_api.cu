@@ -69,6 +69,39 @@ int encode_qkv_maps(const Problem& p, void* tq, void* tk, void* tv, int v_box_co
     return 0;
 }
 
+int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu) {
+    const int NT = (p.S + kChunk - 1) / kChunk;
+    const unsigned long long rows = static_cast<unsigned long long>(p.B) * p.Hv * NT * kChunk;
+    {
+        const unsigned long long d[2] = {128, rows}, s[1] = {256};
+        const unsigned box[2] = {64, 64};
+        if (encode_tma(tw, ws.W, 2, 2, d, s, box, 128)) return 1;
+    }
+    {
+        const unsigned long long d[2] = {64, rows}, s[1] = {128};
+        const unsigned box[2] = {64, 64};
+        if (encode_tma(tp, ws.P, 2, 2, d, s, box, 128)) return 1;
+    }
+    {
+        const unsigned long long d[2] = {128, rows}, s[1] = {512};
+        const unsigned box[2] = {32, 64};
+        if (encode_tma(tu, ws.U, 4, 2, d, s, box, 128)) return 1;
+    }
+    return 0;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 static long long* g_phase_profile = nullptr;
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -208,12 +208,24 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
         };
 
+        // optional cycle accounting by the UMMA-issuing thread of CTA (0,0,0), summed over chunks
+        const bool prof_on = p.prof != nullptr && issuer && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
+        long long prof_t = prof_on ? clock64() : 0;
+#define GDN_PHASE(n)                                   \
+    if (prof_on) {                                     \
+        const long long now_ = clock64();              \
+        prof_acc[n] += now_ - prof_t;                  \
+        prof_t = now_;                                 \
+    }
+
         bool ok = mbar_wait_abortable(&bar_full[0], 0, p.status, kDevTimeoutChainFull, abortp);
         if (ok) load_factors(0);
         tc_fence_before_sync();
         named_bar_sync(2, 128);
         if (issuer && ok) issue_d3(0);
 
+        if (prof_on) prof_t = clock64();
         for (int t = 0; t < NT; ++t) {
             const int s = t % STAGES;
             uint8_t* stg = sm + s * L::kStage;
@@ -221,6 +233,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 // ---- v_new = U - W S, and its decay-scaled copy -------------------------------------------
                 ok = mbar_wait_abortable(&bar_d3, t & 1, p.status, kDevTimeoutChainD3, abortp) && ok;
                 tc_fence_after_sync();
+                GDN_PHASE(0)
                 uint32_t w[32];
                 float x[NV], y[NV];
 #pragma unroll
@@ -245,6 +258,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
                 named_bar_sync(1, 64);
+                GDN_PHASE(1)
                 if (issuer && ok) {
                     tc_fence_after_sync();
                     constexpr uint32_t idesc_kv = umma_idesc_bf16(128, NV, MAJOR_MN, MAJOR_MN);
@@ -266,6 +280,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     umma_commit(&bar_pv[t & 1]);
                     umma_commit(&bar_empty[s]);    // every UMMA that reads this stage has been issued
                 }
+                GDN_PHASE(2)
             } else if (t > 0) {
                 // ---- output rows of the previous chunk, off the critical path ---------------------------------
                 ok = mbar_wait_abortable(&bar_pv[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, kDevTimeoutChainPV, abortp) && ok;
@@ -275,6 +290,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // ---- state rows: S <- exp(gamma_C) S + K^T v~ ------------------------------------------------------
             ok = mbar_wait_abortable(&bar_kv, t & 1, p.status, kDevTimeoutChainKV, abortp) && ok;
             tc_fence_after_sync();
+            GDN_PHASE(3)
             {
                 uint32_t r[32];
 #pragma unroll
@@ -296,8 +312,13 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
             tc_fence_before_sync();
             named_bar_sync(2, 128);
+            GDN_PHASE(4)
             if (issuer && ok && t + 1 < NT) issue_d3(t + 1);
+            GDN_PHASE(5)
         }
+#undef GDN_PHASE
+        if (prof_on)
+            for (int n = 0; n < 6; ++n) p.prof[8 + n] = prof_acc[n];
         if (warp < 2 && NT > 0) {   // output rows of the last chunk
             ok = mbar_wait_abortable(&bar_pv[(NT - 1) & 1], ((NT - 1) >> 1) & 1, p.status, kDevTimeoutChainPV, abortp) && ok;
             tc_fence_after_sync();
@@ -323,23 +344,7 @@ template <int NV, int STAGES>
 int launch_chain_nv(const Problem& p, const Workspace& ws, cudaStream_t stream) {
     alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
-    const int NT = (p.S + kChunk - 1) / kChunk;
-    const unsigned long long rows = static_cast<unsigned long long>(p.B) * p.Hv * NT * kChunk;
-    {
-        const unsigned long long d[2] = {128, rows}, s[1] = {256};
-        const unsigned box[2] = {64, 64};
-        if (encode_tma(&tw, ws.W, 2, 2, d, s, box, 128)) return GDN_ERR_DRIVER;
-    }
-    {
-        const unsigned long long d[2] = {64, rows}, s[1] = {128};
-        const unsigned box[2] = {64, 64};
-        if (encode_tma(&tp, ws.P, 2, 2, d, s, box, 128)) return GDN_ERR_DRIVER;
-    }
-    {
-        const unsigned long long d[2] = {128, rows}, s[1] = {512};
-        const unsigned box[2] = {32, 64};
-        if (encode_tma(&tu, ws.U, 4, 2, d, s, box, 128)) return GDN_ERR_DRIVER;
-    }
+    if (encode_workspace_maps(p, ws, &tw, &tp, &tu)) return GDN_ERR_DRIVER;
     using L = CSmem<NV, STAGES>;
     auto kernel = gdn_chain_kernel<NV, STAGES>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess)

@@ -15,8 +15,10 @@
 // decay folded into the operands; here the pairwise factor exp(gamma_i - gamma_j) <= 1 is used, which
 // stays finite at chunk 64.
 //
-// 106 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and one CTA's
-// tensor-core and TMA latencies hide behind the other's CUDA-core phases.
+// Persistent CTAs (two per SM: 106 KB of shared memory and 256 TMEM columns each) walk the tiles; the
+// next tile's TMA loads and gate reads are issued as soon as the last UMMA of the current tile has
+// finished, W and U leave through swizzled staging tiles and asynchronous TMA stores, and one CTA's
+// tensor-core and memory latencies hide behind its neighbour's CUDA-core phases.
 #include <cuda.h>
 
 #include "../../include/gdn_chunk_sm100.h"
@@ -42,7 +44,8 @@ constexpr uint32_t kPrepTmemCols = 256;   // W | U; the raw K K^T / Q K^T accumu
 template <bool GATE_F32>
 __global__ void __launch_bounds__(128, 2)
 gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, Problem p, Workspace ws) {
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
+                   const __grid_constant__ CUtensorMap tm_u, Problem p, Workspace ws, int NT, long long num_tiles) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sm_u32 = smem_u32(sm);
@@ -52,48 +55,85 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     __shared__ __align__(16) PrepScratch ps;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int t = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
-    const int hq = hv / (p.Hv / p.Hq);
-    const int NT = gridDim.x;
-    const int s0 = t * kChunk;
-    const size_t tile = (static_cast<size_t>(b) * p.Hv + hv) * NT + t;
     const float scale = rsqrtf(static_cast<float>(kD));
+    const int i = tid & 63;
 
+    // Persistent CTA: tiles L = blockIdx.x, blockIdx.x + gridDim.x, ...  L -> (b, chunk t, head hv) with the
+    // head index fastest, so the value heads that share a qk head are prepared at about the same time.
+    struct Tile { int b, t, hv, hq, s0; size_t ws_tile; };
+    auto decode = [&](long long L) {
+        Tile x;
+        x.hv = static_cast<int>(L % p.Hv);
+        x.t = static_cast<int>((L / p.Hv) % NT);
+        x.b = static_cast<int>(L / (static_cast<long long>(p.Hv) * NT));
+        x.hq = x.hv / (p.Hv / p.Hq);
+        x.s0 = x.t * kChunk;
+        x.ws_tile = (static_cast<size_t>(x.b) * p.Hv + x.hv) * NT + x.t;
+        return x;
+    };
+    auto issue_loads = [&](const Tile& x) {   // one thread
+        mbar_arrive_expect_tx(&bar_tma, 6 * 8192);
+        tma_load_4d(sm + PSmem::KQ + 0, &tm_k, &bar_tma, 0, x.hq, x.s0, x.b);        // K, d 0-63   -> rows 0-63
+        tma_load_4d(sm + PSmem::KQ + 16384, &tm_k, &bar_tma, 64, x.hq, x.s0, x.b);   // K, d 64-127
+        tma_load_4d(sm + PSmem::KQ + 8192, &tm_q, &bar_tma, 0, x.hq, x.s0, x.b);     // Q           -> rows 64-127
+        tma_load_4d(sm + PSmem::KQ + 24576, &tm_q, &bar_tma, 64, x.hq, x.s0, x.b);
+        tma_load_4d(sm + PSmem::VT + 0, &tm_v, &bar_tma, 0, x.hv, x.s0, x.b);        // V, dv 0-63
+        tma_load_4d(sm + PSmem::VT + 8192, &tm_v, &bar_tma, 64, x.hv, x.s0, x.b);    // V, dv 64-127
+    };
+
+    // optional cycle accounting by thread 0 of CTA 0, summed over its tiles (slot 15 counts the tiles)
+    const bool prof_on = p.prof != nullptr && tid == 0 && blockIdx.x == 0;
+    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long prof_t = prof_on ? clock64() : 0;
+#define GDN_PHASE(n)                                   \
+    if (prof_on) {                                     \
+        const long long now_ = clock64();              \
+        prof_acc[n] += now_ - prof_t;                  \
+        prof_t = now_;                                 \
+    }
+
+    long long L = blockIdx.x;
+    Tile cur = decode(L);
     if (tid == 0) {
         mbar_init(&bar_tma, 1);
         mbar_init(&bar_mma, 1);
         fence_mbar_init();
-        mbar_arrive_expect_tx(&bar_tma, 6 * 8192);
-        tma_load_4d(sm + PSmem::KQ + 0, &tm_k, &bar_tma, 0, hq, s0, b);        // K, d 0-63   -> rows 0-63
-        tma_load_4d(sm + PSmem::KQ + 16384, &tm_k, &bar_tma, 64, hq, s0, b);   // K, d 64-127
-        tma_load_4d(sm + PSmem::KQ + 8192, &tm_q, &bar_tma, 0, hq, s0, b);     // Q           -> rows 64-127
-        tma_load_4d(sm + PSmem::KQ + 24576, &tm_q, &bar_tma, 64, hq, s0, b);
-        tma_load_4d(sm + PSmem::VT + 0, &tm_v, &bar_tma, 0, hv, s0, b);        // V, dv 0-63
-        tma_load_4d(sm + PSmem::VT + 8192, &tm_v, &bar_tma, 64, hv, s0, b);    // V, dv 64-127
+        issue_loads(cur);
     }
     if (warp == 0) {
         tmem_alloc(&tmem_slot, kPrepTmemCols);
         tmem_relinquish();
     }
+    float gv, bv;
+    prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(cur.b) * p.S + cur.s0, cur.hv, p.Hv,
+                              min(kChunk, p.S - cur.s0), gv, bv);
     float* As = reinterpret_cast<float*>(sm + PSmem::AS);
     float* Tm = reinterpret_cast<float*>(sm + PSmem::TM);
     float* Yt = reinterpret_cast<float*>(sm + PSmem::YT);
-    for (int e = tid; e < kChunk * kSolveStride; e += 128) Tm[e] = 0.f;
-
-    const int valid = min(kChunk, p.S - s0);
-    prep_gates<GATE_F32>(ps, p.g, p.beta, static_cast<size_t>(b) * p.S + s0, hv, p.Hv, valid, scale,
-                         ws.vec + tile * 256);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = tmem_slot;
     const uint32_t lane_base = static_cast<uint32_t>(warp) * 32u;
+    uint32_t ph_tma = 0, ph_mma = 0;
+    bool ok = true;
+    long long tiles_done = 0;
 
-    bool ok = mbar_wait(&bar_tma, 0, p.status, kDevTimeoutTma);
-    ok = __syncthreads_and(ok);
-    uint32_t ph_mma = 0;
+    for (; L < num_tiles && ok; L += gridDim.x) {
+        const size_t tile = cur.ws_tile;
+        // the previous tile's W/U stores must have finished reading their staging buffers
+        if (tid == 0) tma_store_wait_read();
+        prep_gates(ps, gv, bv, scale, ws.vec + tile * 256);
+        prep_zero_upper_blocks(Tm);
+        __syncthreads();
+        GDN_PHASE(0)
 
-    if (ok) {
+        ok = mbar_wait(&bar_tma, ph_tma, p.status, kDevTimeoutTma);
+        ph_tma ^= 1;
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        GDN_PHASE(1)
+
         if (tid == 0) {   // raw K K^T (lanes 0-63) and Q K^T (lanes 64-127)
             tc_fence_after_sync();
             constexpr uint32_t idesc = umma_idesc_bf16(128, 64, MAJOR_K, MAJOR_K);
@@ -107,53 +147,57 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
         ok = __syncthreads_and(ok);
-    }
-    if (ok) {
+        if (!ok) break;
+        GDN_PHASE(2)
+
         tc_fence_after_sync();
-        const int i = tid & 63;
-        float ri, diag[16];
-        prep_row_setup(ps, i, ri, diag);
-        uint32_t r[32];
-        float f[32];
-        if (warp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
-            const float bi = ps.bet[i];
+        {
+            float ri, diag[16];
+            prep_row_setup(ps, i, ri, diag);
+            uint32_t r[32];
+            float f[32];
+            if (warp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
+                const float bi = ps.bet[i];
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
-                prep_row_factors(ps, i, half, ri, diag, f);
-                tmem_ld_wait();
+                for (int half = 0; half < 2; ++half) {
+                    tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
+                    prep_row_factors(ps, i, half, ri, diag, f);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    float4 o;
-                    o.x = (half * 32 + c + 0 < i) ? bi * f[c + 0] * __uint_as_float(r[c + 0]) : 0.f;
-                    o.y = (half * 32 + c + 1 < i) ? bi * f[c + 1] * __uint_as_float(r[c + 1]) : 0.f;
-                    o.z = (half * 32 + c + 2 < i) ? bi * f[c + 2] * __uint_as_float(r[c + 2]) : 0.f;
-                    o.w = (half * 32 + c + 3 < i) ? bi * f[c + 3] * __uint_as_float(r[c + 3]) : 0.f;
-                    *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
+                    for (int c = 0; c < 32; c += 4) {
+                        float4 o;
+                        o.x = (half * 32 + c + 0 < i) ? bi * f[c + 0] * __uint_as_float(r[c + 0]) : 0.f;
+                        o.y = (half * 32 + c + 1 < i) ? bi * f[c + 1] * __uint_as_float(r[c + 1]) : 0.f;
+                        o.z = (half * 32 + c + 2 < i) ? bi * f[c + 2] * __uint_as_float(r[c + 2]) : 0.f;
+                        o.w = (half * 32 + c + 3 < i) ? bi * f[c + 3] * __uint_as_float(r[c + 3]) : 0.f;
+                        *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
+                    }
                 }
-            }
-        } else {          // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
-            __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
+            } else {          // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
+                __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
-                prep_row_factors(ps, i, half, ri, diag, f);
-                tmem_ld_wait();
+                for (int half = 0; half < 2; ++half) {
+                    tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
+                    prep_row_factors(ps, i, half, ri, diag, f);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint4 pk;
-                    pk.x = pack_bf16x2(scale * f[8 * ch + 0] * __uint_as_float(r[8 * ch + 0]), scale * f[8 * ch + 1] * __uint_as_float(r[8 * ch + 1]));
-                    pk.y = pack_bf16x2(scale * f[8 * ch + 2] * __uint_as_float(r[8 * ch + 2]), scale * f[8 * ch + 3] * __uint_as_float(r[8 * ch + 3]));
-                    pk.z = pack_bf16x2(scale * f[8 * ch + 4] * __uint_as_float(r[8 * ch + 4]), scale * f[8 * ch + 5] * __uint_as_float(r[8 * ch + 5]));
-                    pk.w = pack_bf16x2(scale * f[8 * ch + 6] * __uint_as_float(r[8 * ch + 6]), scale * f[8 * ch + 7] * __uint_as_float(r[8 * ch + 7]));
-                    *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint4 pk;
+                        pk.x = pack_bf16x2(scale * f[8 * ch + 0] * __uint_as_float(r[8 * ch + 0]), scale * f[8 * ch + 1] * __uint_as_float(r[8 * ch + 1]));
+                        pk.y = pack_bf16x2(scale * f[8 * ch + 2] * __uint_as_float(r[8 * ch + 2]), scale * f[8 * ch + 3] * __uint_as_float(r[8 * ch + 3]));
+                        pk.z = pack_bf16x2(scale * f[8 * ch + 4] * __uint_as_float(r[8 * ch + 4]), scale * f[8 * ch + 5] * __uint_as_float(r[8 * ch + 5]));
+                        pk.w = pack_bf16x2(scale * f[8 * ch + 6] * __uint_as_float(r[8 * ch + 6]), scale * f[8 * ch + 7] * __uint_as_float(r[8 * ch + 7]));
+                        *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
+                    }
                 }
             }
         }
         tc_fence_before_sync();
         __syncthreads();
+        GDN_PHASE(3)
 
         prep_invert_unit_lower(As, Tm, Yt);
+        GDN_PHASE(4)
 
         {   // [T diag(beta e^gamma) ; T diag(beta)] as one 128-row K-major operand
             const int which = tid >> 6;
@@ -161,6 +205,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         fence_proxy_async_smem();
         __syncthreads();
+        GDN_PHASE(5)
 
         if (tid == 0) {   // W = T' K (lanes 0-63, columns 0-127), U = T'' V (lanes 64-127, columns 128-255)
             tc_fence_after_sync();
@@ -174,47 +219,80 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
                 const uint64_t ad = umma_smem_desc(sm_u32 + PSmem::TS + ks * 32, 16, 1024, SWZ_128B);
-                const uint64_t bv = umma_smem_desc(sm_u32 + PSmem::VT + ks * 2048, 8192, 1024, SWZ_128B);
-                umma_bf16_ss(tmem + 128, ad, bv, idesc, ks > 0);
+                const uint64_t bv_ = umma_smem_desc(sm_u32 + PSmem::VT + ks * 2048, 8192, 1024, SWZ_128B);
+                umma_bf16_ss(tmem + 128, ad, bv_, idesc, ks > 0);
             }
             umma_commit(&bar_mma);
         }
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
         ok = __syncthreads_and(ok);
-    }
-    if (ok) {
+        if (!ok) break;
+        GDN_PHASE(6)
+
+        // every tile buffer is free again: start the next tile's loads and gate reads before the epilogue
+        const long long Ln = L + gridDim.x;
+        Tile nxt = cur;
+        if (Ln < num_tiles) {
+            nxt = decode(Ln);
+            if (tid == 0) issue_loads(nxt);
+            prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(nxt.b) * p.S + nxt.s0, nxt.hv, p.Hv,
+                                      min(kChunk, p.S - nxt.s0), gv, bv);
+        }
+
+        // epilogue: W (bf16) and U (fp32) into swizzled staging tiles, then TMA stores to the workspace
         tc_fence_after_sync();
-        const int i = tid & 63;
-        uint32_t r[32];
-        if (warp < 2) {
-            __nv_bfloat16* wrow = ws.W + tile * (kChunk * kD) + static_cast<size_t>(i) * kD;
+        {
+            uint32_t r[32];
+            if (warp < 2) {
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                tmem_ld_x32(tmem_addr(tmem, lane_base, q4 * 32), r);
-                tmem_ld_wait();
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    tmem_ld_x32(tmem_addr(tmem, lane_base, q4 * 32), r);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint4 pk;
-                    pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
-                    pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
-                    pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
-                    pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-                    *reinterpret_cast<uint4*>(wrow + q4 * 32 + 8 * ch) = pk;
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint4 pk;
+                        pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                        pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                        pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                        pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                        *reinterpret_cast<uint4*>(sm + PSmem::TS + (q4 >> 1) * 8192 +
+                                                  swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    tmem_ld_x32(tmem_addr(tmem, lane_base, 128 + q4 * 32), r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4*>(sm + PSmem::AS + q4 * 8192 + swz_chunk_offset<128>(i, c)) =
+                            make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
                 }
             }
-        } else {
-            float* urow = ws.U + tile * (kChunk * kD) + static_cast<size_t>(i) * kD;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                tmem_ld_x32(tmem_addr(tmem, lane_base, 128 + q4 * 32), r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 32; c += 4)
-                    *reinterpret_cast<uint4*>(urow + q4 * 32 + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
-            }
         }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncthreads();
+        if (tid == 0) {
+            const int row0 = static_cast<int>(tile * kChunk);
+            tma_store_2d(&tm_w, sm + PSmem::TS, 0, row0);
+            tma_store_2d(&tm_w, sm + PSmem::TS + 8192, 64, row0);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) tma_store_2d(&tm_u, sm + PSmem::AS + q4 * 8192, q4 * 32, row0);
+            tma_store_commit();
+        }
+        GDN_PHASE(7)
+        cur = nxt;
+        ++tiles_done;
     }
+#undef GDN_PHASE
+    if (prof_on) {
+        for (int n = 0; n < 8; ++n) p.prof[n] = prof_acc[n];
+        p.prof[15] = tiles_done;
+    }
+    if (tid == 0) tma_store_wait_all();
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, kPrepTmemCols);
@@ -223,14 +301,17 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 }  // namespace
 
 int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream) {
-    alignas(64) CUtensorMap tq, tk, tv;
+    alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
+    if (encode_workspace_maps(p, ws, &tw, &tp, &tu)) return GDN_ERR_DRIVER;
     const int NT = (p.S + kChunk - 1) / kChunk;
+    const long long tiles = static_cast<long long>(p.B) * p.Hv * NT;
+    const long long max_ctas = 2ll * sm_count();
+    const unsigned grid = static_cast<unsigned>(tiles < max_ctas ? tiles : max_ctas);
     auto go = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PSmem::kDynamic) != cudaSuccess)
             return GDN_ERR_CUDA;
-        const dim3 grid(NT, p.Hv, p.B), block(128);
-        kernel<<<grid, block, PSmem::kDynamic, stream>>>(tq, tk, tv, p, ws);
+        kernel<<<grid, 128, PSmem::kDynamic, stream>>>(tq, tk, tv, tw, tu, p, ws, NT, tiles);
         count_launch();
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };

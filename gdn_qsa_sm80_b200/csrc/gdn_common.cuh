@@ -77,6 +77,10 @@ inline int encode_tma_bf16(void* tmap_out, const void* base, int rank, const uns
                            const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes) {
     return encode_tma(tmap_out, base, 2, rank, dims, strides_bytes, box, swizzle_bytes);
 }
+// TMA descriptors of the workspace arrays W (bf16, 64x64 boxes), P (bf16, 64x64) and U (fp32, 32x64 boxes).
+int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu);
+// Number of SMs of the current device (cached per device).
+int sm_count();
 // TMA descriptors of q, k ([B,S,Hq,128], 64x64 boxes) and v ([B,S,Hv,128], v_box_cols x 64 boxes).
 int encode_qkv_maps(const Problem& p, void* tq, void* tk, void* tv, int v_box_cols);
 

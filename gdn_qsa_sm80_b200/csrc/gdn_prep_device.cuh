@@ -30,22 +30,28 @@ __device__ __forceinline__ float prep_load_gate(const void* p, size_t idx) {
     return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
 }
 
-// Gate cumsum over the chunk by warp shuffles (threads 0-63 hold one token each) and the decay tables.
+// Loads the log gate and the update gate of token `tid` of a chunk (threads 0-63; zeros for padding).
+template <bool GATE_F32>
+__device__ __forceinline__ void prep_load_gates(const void* g, const void* beta, size_t tok0, int hv, int Hv,
+                                                int valid, float& gv, float& bv) {
+    const int tid = threadIdx.x;
+    gv = 0.f;
+    bv = 0.f;
+    if (tid < valid) {
+        const size_t idx = (tok0 + tid) * Hv + hv;
+        gv = prep_load_gate<GATE_F32>(g, idx);
+        bv = prep_load_gate<GATE_F32>(beta, idx);
+    }
+}
+
+// Gate cumsum over the chunk by warp shuffles (threads 0-63 hold one token each: gv, bv) and the decay tables.
 // Contains two __syncthreads(); a third one is needed before the tables are read.
 // If vec_out != nullptr, also writes the per-token factors a later kernel needs:
 //   vec_out[i] = exp(gamma_C - gamma_i), vec_out[64+i] = scale * exp(gamma_i), vec_out[128] = exp(gamma_C).
-template <bool GATE_F32>
-__device__ __forceinline__ void prep_gates(PrepScratch& ps, const void* g, const void* beta, size_t tok0, int hv,
-                                           int Hv, int valid, float scale, float* vec_out) {
+__device__ __forceinline__ void prep_gates(PrepScratch& ps, float gv, float bv, float scale, float* vec_out) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    float gsum = 0.f, bv = 0.f;
+    float gsum = 0.f;
     if (tid < kChunk) {
-        float gv = 0.f;
-        if (tid < valid) {
-            const size_t idx = (tok0 + tid) * Hv + hv;
-            gv = prep_load_gate<GATE_F32>(g, idx);
-            bv = prep_load_gate<GATE_F32>(beta, idx);
-        }
         gsum = gv;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -90,9 +96,14 @@ __device__ __forceinline__ void prep_row_factors(const PrepScratch& ps, int i, i
     for (int J2 = 0; J2 < 2; ++J2) {
         const int J = half * 2 + J2;
 #pragma unroll
-        for (int jj = 0; jj < 16; ++jj) {
-            const float off = ri * ct[16 * J + jj];
-            f[16 * J2 + jj] = (J < I) ? off : ((J == I) ? diag[jj] : 0.f);
+        for (int q = 0; q < 4; ++q) {
+            const float4 c4 = *reinterpret_cast<const float4*>(ct + 16 * J + 4 * q);
+            const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int jj = 4 * q + u;
+                f[16 * J2 + jj] = (J < I) ? ri * cv[u] : ((J == I) ? diag[jj] : 0.f);
+            }
         }
     }
 }
@@ -237,6 +248,20 @@ __device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* T
             store_c_frag(Tm + (32 + 16 * rb) * kSolveStride + 16 * cb + 8 * nt, kSolveStride, lane, acc2[nt], -1.f);
     }
     __syncthreads();
+}
+
+// Zeroes the six 16x16 blocks of `Tm` above the block diagonal (all 128 threads; what prep_invert_unit_lower
+// expects on entry).
+__device__ __forceinline__ void prep_zero_upper_blocks(float* Tm) {
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int e = 0; e < 3; ++e) {
+        const int idx = tid + 128 * e;              // 384 float4 = 6 blocks x 16 rows x 4 float4
+        const int blk = idx >> 6, r = (idx >> 2) & 15, q = idx & 3;
+        const int I = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
+        const int J = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+        *reinterpret_cast<float4*>(Tm + (16 * I + r) * kSolveStride + 16 * J + 4 * q) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 }
 
 // Row `i` of  T diag(f)  as bf16 into row `dst_row` of a 128-byte-swizzled K-major tile
