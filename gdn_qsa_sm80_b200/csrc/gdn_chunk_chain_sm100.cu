@@ -12,12 +12,15 @@
 // (csrc/gdn_chunk/gdn_kernel.cu:1027-1224) with mma.sync and a bf16 state; here the products are
 // tcgen05 UMMAs with fp32 accumulators in TMEM and the state stays fp32.
 //
-// Roles (160 threads): warps 0-3 own the four TMEM lane quadrants and do all epilogues; warp 2's
-// first lane also issues every UMMA; warp 4's first lane is the TMA producer that keeps a ring of
-// STAGES chunks (K, [Q;W], P, U slice, per-token factors) in flight.  Only D3 -> v_new -> D5 ->
+// Roles (192 threads): warps 0-3 own the four TMEM lane quadrants and do all epilogues; warp 2's
+// first lane issues the UMMAs of the critical path (D3, D5); warp 5's first lane issues D4, which
+// nothing on the critical path waits for; warp 4's first lane is the TMA producer that keeps a ring
+// of STAGES chunks (K, [Q;W], P, U slice, per-token factors) in flight.  Only D3 -> v_new -> D5 ->
 // state sits on the critical path: the output epilogue of chunk t-1 runs on warps 0-1 while
 // warps 2-3 turn W S into v_new for chunk t, and accumulators are double-buffered so the next D3
-// never waits for an output epilogue.
+// never waits for an output epilogue.  (A UMMA with N <= 64 occupies the tensor pipe for about 40
+// cycles whatever N is, and issuing from several warps does not raise that rate, so what counts on
+// the critical path is the number of UMMA instructions: 8 for D3, 4 for D5.)
 #include <cuda.h>
 
 #include "../../include/gdn_chunk_sm100.h"
@@ -54,6 +57,7 @@ constexpr int kDevTimeoutChainEmpty = 0x202;
 constexpr int kDevTimeoutChainD3 = 0x203;
 constexpr int kDevTimeoutChainKV = 0x204;
 constexpr int kDevTimeoutChainPV = 0x205;
+constexpr int kDevTimeoutChainVN = 0x206;
 
 template <int NV>
 __device__ __forceinline__ void store_row_bf16(uint8_t* tile, uint32_t row, const float* x) {
@@ -69,7 +73,7 @@ __device__ __forceinline__ void store_row_bf16(uint8_t* tile, uint32_t row, cons
 }
 
 template <int NV, int STAGES>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(192, 1)
 gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_p,
                  const __grid_constant__ CUtensorMap tm_u, Problem p, Workspace ws) {
@@ -82,6 +86,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __shared__ __align__(8) uint64_t bar_empty[STAGES];
     __shared__ __align__(8) uint64_t bar_d3, bar_kv;
     __shared__ __align__(8) uint64_t bar_pv[2];
+    __shared__ __align__(8) uint64_t bar_vn;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -100,8 +105,9 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_empty[s], 1);
+            mbar_init(&bar_empty[s], 2);   // D5 seen complete by a chain thread + D4 complete (commit)
         }
+        mbar_init(&bar_vn, 1);
         mbar_init(&bar_d3, 1);
         mbar_init(&bar_kv, 1);
         mbar_init(&bar_pv[0], 1);
@@ -146,6 +152,25 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 bulk_load_1d(st + L::VEC, ws.vec + (tile0 + t) * 256, 1024, &bar_full[s]);
             }
         }
+    } else if (warp == 5) {
+        // ------------------------------- off-critical-path UMMA issuer: D4 = P v_new -----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(128, NV, MAJOR_K, MAJOR_MN);
+            for (int t = 0; t < NT; ++t) {
+                const int s = t % STAGES;
+                if (!mbar_wait_abortable(&bar_vn, t & 1, p.status, kDevTimeoutChainVN, abortp)) break;
+                tc_fence_after_sync();
+                const uint32_t sb = sm_u32 + s * L::kStage;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint64_t ad = umma_smem_desc(sb + L::PB + ks * 32, 16, 1024, SWZ_128B);
+                    const uint64_t bd = umma_smem_desc(sm_u32 + L::VN + ks * 16 * L::kRowBytes, 16384, 8 * L::kRowBytes, L::kSwz);
+                    umma_bf16_ss(tmem + kColPV + (t & 1) * NV, ad, bd, idesc_pv, ks > 0);
+                }
+                umma_commit(&bar_pv[t & 1]);
+                umma_commit(&bar_empty[s]);    // second arrival: the P tile of this stage has been consumed
+            }
+        }
     } else {
         // ------------------------------- chain warps ---------------------------------------------------
         const uint32_t lane_base = static_cast<uint32_t>(warp) * 32u;
@@ -169,16 +194,19 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             f_tok = (warp < 2) ? vec[kChunk + i] : vec[i];     // warps 0-1: scale e^gamma_i ; warps 2-3: e^{gamma_C-gamma_i}
             dC = vec[2 * kChunk];
         };
+        const uint64_t sb_desc0 = umma_smem_desc(sm_u32 + L::SB, 16384, 8 * L::kRowBytes, L::kSwz);
+        const uint64_t vs_desc0 = umma_smem_desc(sm_u32 + L::VS, 16384, 8 * L::kRowBytes, L::kSwz);
         auto issue_d3 = [&](int t) {
             const uint32_t sb = sm_u32 + (t % STAGES) * L::kStage;
             constexpr uint32_t idesc = umma_idesc_bf16(128, NV, MAJOR_K, MAJOR_MN);
+            // descriptors differ only in the start-address field (bytes >> 4 in the low bits)
+            const uint64_t a0 = umma_smem_desc(sb + L::QW, 16, 1024, SWZ_128B);
+            const uint32_t d = tmem + kColD3 + (t & 1) * NV;
             tc_fence_after_sync();
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                const uint64_t ad = umma_smem_desc(sb + L::QW + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, SWZ_128B);
-                const uint64_t bd = umma_smem_desc(sm_u32 + L::SB + ks * 16 * L::kRowBytes, 16384, 8 * L::kRowBytes, L::kSwz);
-                umma_bf16_ss(tmem + kColD3 + (t & 1) * NV, ad, bd, idesc, ks > 0);
-            }
+            for (int ks = 0; ks < 8; ++ks)
+                umma_bf16_ss(d, a0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), sb_desc0 + ((ks * 16 * L::kRowBytes) >> 4),
+                             idesc, ks > 0);
             umma_commit(&bar_d3);
         };
         auto out_epilogue = [&](int t, float qf) {   // rows of chunk t: O = qf * (Q S) + P v_new
@@ -253,6 +281,8 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         y[part * 32 + c] = vn * f_tok;
                     }
                 }
+                if (t > 0)   // D4 of the previous chunk must have finished reading v_new
+                    ok = mbar_wait_abortable(&bar_pv[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, kDevTimeoutChainPV, abortp) && ok;
                 store_row_bf16<NV>(sm + L::VN, i, x);
                 store_row_bf16<NV>(sm + L::VS, i, y);
                 fence_proxy_async_smem();
@@ -260,25 +290,15 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 named_bar_sync(1, 64);
                 GDN_PHASE(1)
                 if (issuer && ok) {
-                    tc_fence_after_sync();
                     constexpr uint32_t idesc_kv = umma_idesc_bf16(128, NV, MAJOR_MN, MAJOR_MN);
-                    constexpr uint32_t idesc_pv = umma_idesc_bf16(128, NV, MAJOR_K, MAJOR_MN);
-                    const uint32_t sb = sm_u32 + s * L::kStage;
+                    const uint64_t k0 = umma_smem_desc(sm_u32 + s * L::kStage + L::KT, 8192, 1024, SWZ_128B);
+                    tc_fence_after_sync();
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t ad = umma_smem_desc(sb + L::KT + ks * 2048, 8192, 1024, SWZ_128B);
-                        const uint64_t bd = umma_smem_desc(sm_u32 + L::VS + ks * 16 * L::kRowBytes, 16384, 8 * L::kRowBytes, L::kSwz);
-                        umma_bf16_ss(tmem + kColKV, ad, bd, idesc_kv, ks > 0);
-                    }
+                    for (int ks = 0; ks < 4; ++ks)
+                        umma_bf16_ss(tmem + kColKV, k0 + ((ks * 2048) >> 4), vs_desc0 + ((ks * 16 * L::kRowBytes) >> 4),
+                                     idesc_kv, ks > 0);
                     umma_commit(&bar_kv);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t ad = umma_smem_desc(sb + L::PB + ks * 32, 16, 1024, SWZ_128B);
-                        const uint64_t bd = umma_smem_desc(sm_u32 + L::VN + ks * 16 * L::kRowBytes, 16384, 8 * L::kRowBytes, L::kSwz);
-                        umma_bf16_ss(tmem + kColPV + (t & 1) * NV, ad, bd, idesc_pv, ks > 0);
-                    }
-                    umma_commit(&bar_pv[t & 1]);
-                    umma_commit(&bar_empty[s]);    // every UMMA that reads this stage has been issued
+                    mbar_arrive(&bar_vn);          // v_new is in shared memory: warp 5 may issue D4
                 }
                 GDN_PHASE(2)
             } else if (t > 0) {
@@ -290,6 +310,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // ---- state rows: S <- exp(gamma_C) S + K^T v~ ------------------------------------------------------
             ok = mbar_wait_abortable(&bar_kv, t & 1, p.status, kDevTimeoutChainKV, abortp) && ok;
             tc_fence_after_sync();
+            if (tid == 0 && ok) mbar_arrive(&bar_empty[s]);   // first arrival: D3 and D5 of this stage are complete
             GDN_PHASE(3)
             {
                 uint32_t r[32];
@@ -349,7 +370,7 @@ int launch_chain_nv(const Problem& p, const Workspace& ws, cudaStream_t stream) 
     auto kernel = gdn_chain_kernel<NV, STAGES>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess)
         return GDN_ERR_CUDA;
-    const dim3 grid(kD / NV, p.Hv, p.B), block(160);
+    const dim3 grid(kD / NV, p.Hv, p.B), block(192);
     kernel<<<grid, block, L::kDynamic, stream>>>(tq, tk, tw, tp, tu, p, ws);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
