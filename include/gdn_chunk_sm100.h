@@ -81,6 +81,19 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
                         int B, int S, int Hq, int Hv, int gate_dtype, int path, void* stream);
 
 /*
+ * Second level of the two-level chunk scan.  A [n_seq][G][128][128] and Bm (same shape), fp32: group g
+ * of sequence s maps its incoming state to its outgoing state by S_out = A S_in + Bm.  Writes the
+ * state every group starts from into s_in [n_seq][G][128][128] and the state after the last group
+ * into s_final [n_seq][128][128] (may be NULL); h0 [n_seq][128][128] is the state before group 0
+ * (NULL = zeros).  n_seq = batch * value heads (<= 65535).  Launches on `stream`, does not wait.
+ * Replaces the reference's affine prefix scans over (A_g, B_g): gdn_scan_stage2
+ * (csrc/gdn_chunk/gdn_scan_stage2.cu:228) and gdn_scan_stage2_blelloch
+ * (csrc/gdn_chunk/gdn_scan_stage2_blelloch.cu:487-522).
+ */
+int gdn_chunk_scan_transfers(const float* A, const float* Bm, const float* h0, float* s_in, float* s_final,
+                             int n_seq, int G, void* stream);
+
+/*
  * Synchronises `stream`, then copies the device status word kept at the start of `scratch` into
  * *device_status (0 = no kernel reported a problem).  Returns GDN_ERR_DEVICE when it is non-zero.
  * Counterpart of C10_CUDA_KERNEL_LAUNCH_CHECK after the reference's launches
