@@ -36,6 +36,7 @@ EXPORTS = (
     "gdn_chunk_scratch_bytes",
     "gdn_chunk_workspace_offsets",
     "gdn_chunk_fwd_sm100",
+    "gdn_chunk_fwd_sm100_noalloc",
     "gdn_chunk_scan_transfers",
     "gdn_chunk_read_status",
     "gdn_chunk_error_string",
@@ -69,6 +70,8 @@ def load() -> ctypes.CDLL:
     lib.gdn_chunk_workspace_offsets.restype = ci
     lib.gdn_chunk_fwd_sm100.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, vp]
     lib.gdn_chunk_fwd_sm100.restype = ci
+    lib.gdn_chunk_fwd_sm100_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]
+    lib.gdn_chunk_fwd_sm100_noalloc.restype = ci
     lib.gdn_chunk_scan_transfers.argtypes = [vp, vp, vp, vp, vp, ci, ci, vp]
     lib.gdn_chunk_scan_transfers.restype = ci
     lib.gdn_chunk_read_status.argtypes = [vp, vp, ctypes.POINTER(ci)]

@@ -215,6 +215,48 @@ const char* gdn_chunk_error_string(int status) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Forward pass for callers that cannot provide scratch memory.
+//
+// Some hosts of this library may not allocate device memory at all when they call it: a serving
+// runtime that reserved its whole memory budget at start-up and hands out fixed buffers for inputs
+// and outputs only, or a latency-critical loop in which cudaMalloc (which synchronises the whole
+// device) must never run.  For them the workspace of the prepare + chain path lives in the array
+// below, which every GPU that loads this library holds until the process exits.
+//
+// `g_noalloc_scratch` is a HOST-side handle in host code, not a device address; its device address
+// is looked up once per device with cudaGetSymbolAddress (with that device current) and kept in
+// g_noalloc_addr.  All calls on a device share the one array: the status word at its start is cleared
+// by every call, everything else is fully rewritten before it is read, and two calls that overlap on
+// the GPU (different streams) would race on it.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocBytes = 16u << 20;   // 16 MiB: up to 287 (batch x value head x 64-token chunk) tiles
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+static void* g_noalloc_addr[64] = {nullptr};
+static std::mutex g_noalloc_mutex;
+
+int gdn_chunk_fwd_sm100_noalloc(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                                const float* h0, void* out, float* hT, int B, int S, int Hq, int Hv,
+                                int gate_dtype, void* stream) {
+    if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
+    // reject problems whose workspace does not fit the fixed array (the caller gets a clear status, nothing runs)
+    if (gdn_chunk_scratch_bytes(B, S, Hq, Hv, GDN_PATH_AUTO) > kNoAllocBytes) return GDN_ERR_SCRATCH;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GDN_ERR_CUDA;
+    void* addr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_addr[dev]) {   // first call on this device: one-time set-up
+            void* ptr = nullptr;
+            if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) return GDN_ERR_CUDA;
+            g_noalloc_addr[dev] = ptr;
+        }
+        addr = g_noalloc_addr[dev];
+    }
+    return gdn_chunk_fwd_sm100(q, k, v, g, beta, h0, out, hT, addr, kNoAllocBytes, B, S, Hq, Hv, gate_dtype,
+                               GDN_PATH_AUTO, stream);
+}
+
 void gdn_chunk_set_phase_profile(void* device_buffer) { g_phase_profile = static_cast<long long*>(device_buffer); }
 
 unsigned long long gdn_chunk_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -94,6 +94,25 @@ int gdn_chunk_scan_transfers(const float* A, const float* Bm, const float* h0, f
                              int n_seq, int G, void* stream);
 
 /*
+ * The same forward pass for callers that cannot hand over scratch memory and must not trigger an
+ * allocation: for instance a serving runtime that carved up all device memory at start-up and only
+ * passes fixed input/output buffers to its plugins, or a latency-critical loop where cudaMalloc (a
+ * device-wide synchronisation) is not acceptable.  The workspace is a fixed 16 MiB array inside the
+ * library's device image (held by every GPU that loads the library, for the life of the process), so
+ * the problem must satisfy  B * Hv * ceil(S/64) <= 287  (e.g. 4 value heads x 4096 tokens); larger
+ * problems return GDN_ERR_SCRATCH and launch nothing.  Arguments and results are those of
+ * gdn_chunk_fwd_sm100 with path = GDN_PATH_AUTO.  The call itself allocates nothing.
+ * The first call on each device looks up the array's device address (a one-time set-up step); make
+ * that first call outside any stream capture.  All calls on a device share the array: do not let two
+ * of them overlap on the GPU (e.g. on different streams).
+ * This entry point has no counterpart in the reference, which allocates its workspaces with torch
+ * inside every call.
+ */
+int gdn_chunk_fwd_sm100_noalloc(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                                const float* h0, void* out, float* hT, int B, int S, int Hq, int Hv,
+                                int gate_dtype, void* stream);
+
+/*
  * Synchronises `stream`, then copies the device status word kept at the start of `scratch` into
  * *device_status (0 = no kernel reported a problem).  Returns GDN_ERR_DEVICE when it is non-zero.
  * Counterpart of C10_CUDA_KERNEL_LAUNCH_CHECK after the reference's launches
