@@ -1,0 +1,137 @@
+"""Multi-GPU use of gdn_chunk: one process per GPU, `torch.distributed` for the plumbing.
+
+The reference has no distributed code at all; this module is new.  Two cases:
+
+* Independent sequences (`plan_shards`, `shard_inputs`): every (batch, value head) pair is its own
+  recurrence (the reference's grids are (B, H, ...), csrc/gdn_chunk/gdn_kernel.cu:2892), so B x Hv is
+  split over the ranks - batch first, then value heads in whole qk groups so q/k are never duplicated -
+  and NO communication is needed.
+* One long sequence (`sequence_parallel_forward`): the sequence is cut into contiguous segments, one per
+  rank; the 128x128 fp32 boundary states per value head are passed rank to rank with send/recv (NCCL over
+  NVLink on GPUs, gloo in the CPU tests).  Splitting a sequence and chaining states is exact.
+  mode="pipeline": rank r waits for its incoming state, runs, sends its final state (serial, 1x work).
+  mode="scan":     every rank first computes its segment's affine transfer S_out = A S_in + B
+                   (B: final state from zeros; A: final state from identity with zero values), then the
+                   states ripple down the ranks (one small matrix product per hop), then every rank runs
+                   its segment from its true incoming state - all ranks busy at once, 3x work per rank.
+The received state always lands in this rank's own memory before any kernel reads it.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+__all__ = ["Shard", "plan_shards", "shard_inputs", "sequence_parallel_forward", "segment_bounds"]
+
+
+@dataclass(frozen=True)
+class Shard:
+    b0: int
+    b1: int
+    hv0: int
+    hv1: int
+
+    @property
+    def units(self) -> int:
+        return (self.b1 - self.b0) * (self.hv1 - self.hv0)
+
+
+def plan_shards(B: int, Hq: int, Hv: int, world: int) -> list[Shard]:
+    """Partition the B x Hv independent sequences evenly over `world` ranks.
+
+    Batch is split first; when world > B (or does not divide it) the remaining factor splits the value
+    heads in whole qk groups (Hv // Hq value heads share one qk head).  Raises ValueError when no even
+    partition exists.
+    """
+    if world <= 0 or B <= 0 or Hq <= 0 or Hv <= 0 or Hv % Hq:
+        raise ValueError("bad shape")
+    import math
+    nb = math.gcd(B, world)          # ranks along the batch
+    nh = world // nb                 # ranks along the heads
+    if Hq % nh:
+        raise ValueError(f"cannot split B={B}, Hq={Hq} evenly over {world} ranks")
+    rep = Hv // Hq
+    bs, hs = B // nb, (Hq // nh) * rep
+    return [Shard(ib * bs, (ib + 1) * bs, ih * hs, (ih + 1) * hs) for ib in range(nb) for ih in range(nh)]
+
+
+def shard_inputs(q, k, v, g, beta, h0, shard: Shard):
+    """This rank's slice of every tensor (views; the operator makes them contiguous)."""
+    rep = v.shape[2] // q.shape[2]
+    hq0, hq1 = shard.hv0 // rep, shard.hv1 // rep
+    sb = slice(shard.b0, shard.b1)
+    out = (q[sb, :, hq0:hq1], k[sb, :, hq0:hq1], v[sb, :, shard.hv0:shard.hv1], g[sb, :, shard.hv0:shard.hv1],
+           beta[sb, :, shard.hv0:shard.hv1], None if h0 is None else h0[sb, shard.hv0:shard.hv1])
+    return out
+
+
+def segment_bounds(S: int, world: int, chunk: int = 64) -> list[tuple[int, int]]:
+    """Contiguous token ranges, one per rank, every boundary a multiple of the chunk size."""
+    nt = (S + chunk - 1) // chunk
+    per, extra = divmod(nt, world)
+    bounds, c = [], 0
+    for r in range(world):
+        n = per + (1 if r < extra else 0)
+        bounds.append((min(c * chunk, S), min((c + n) * chunk, S)))
+        c += n
+    return bounds
+
+
+def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, mode="pipeline", compute=None,
+                              timeout_s: float | None = None):
+    """Forward over THIS rank's contiguous segment of one long sequence.
+
+    q..beta: the segment's tensors ([B, S_seg, H, ...]); initial_state: state before the whole sequence
+    (only rank 0's is used).  `compute(q, k, v, g, beta, initial_state) -> (out, final_state)` defaults to
+    the CUDA operator.  Returns (out_segment, final_state); the final state is the whole sequence's on the
+    last rank and this segment's outgoing state elsewhere.
+    """
+    if compute is None:
+        from .gdn_chunk_interface import gdn_chunk
+
+        def compute(q_, k_, v_, g_, b_, h_):
+            return gdn_chunk(q_, k_, v_, g_, b_, output_final_state=True, initial_state=h_)
+
+    rank = dist.get_rank(group)
+    world = dist.get_world_size(group)
+    B, Hv, D = v.shape[0], v.shape[2], v.shape[3]
+    dev = v.device
+    shape = (B, Hv, D, D)
+
+    def recv_state():
+        buf = torch.empty(shape, dtype=torch.float32, device=dev)
+        dist.recv(buf, src=dist.get_global_rank(group, rank - 1) if group is not None else rank - 1, group=group)
+        return buf
+
+    def send_state(s):
+        dist.send(s.to(torch.float32).contiguous(), dst=dist.get_global_rank(group, rank + 1) if group is not None else rank + 1,
+                  group=group)
+
+    if mode == "pipeline":
+        s_in = initial_state if rank == 0 else recv_state()
+        out, s_out = compute(q, k, v, g, beta, s_in)
+        if rank + 1 < world:
+            send_state(s_out)
+        return out, s_out
+    if mode != "scan":
+        raise ValueError(f"unknown mode {mode!r}")
+    # pass A: this segment's affine transfer, computed by every rank at the same time
+    _, b_seg = compute(q, k, v, g, beta, None)
+    a_seg = None
+    if rank + 1 < world:     # the last rank never forwards a state, so it needs no transfer matrix
+        eye = torch.eye(D, dtype=torch.float32, device=dev).expand(shape).contiguous()
+        _, a_seg = compute(q, k, torch.zeros_like(v), g, beta, eye)
+    # exchange: ripple the true states down the ranks
+    if rank == 0:
+        s_in = None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32)
+    else:
+        s_in = recv_state()
+    if rank + 1 < world:
+        s_out = b_seg.to(torch.float32) if s_in is None else torch.matmul(a_seg.to(torch.float32), s_in) + b_seg.to(torch.float32)
+        send_state(s_out)
+    # pass B: the segment from its true incoming state
+    out, s_fin = compute(q, k, v, g, beta, s_in)
+    return out, s_fin

@@ -21,7 +21,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["gdn_chunk", "gdn_chunk_twolevel", "gdn_chunk_reference", "GDN_D", "GDN_CHUNK"]
+__all__ = ["gdn_chunk", "gdn_chunk_twolevel", "gdn_chunk_reference", "scan_transfers", "GDN_D", "GDN_CHUNK"]
 
 GDN_D = 128      # head dim (compile-time constant in the kernels)
 GDN_CHUNK = 64   # intra-chunk size (compile-time constant)
@@ -126,16 +126,60 @@ def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, pat
     return _forward(q, k, v, g, beta, output_final_state, initial_state, path)
 
 
-def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt_eps=1e-2):
-    """Kept for call-site compatibility with the reference (gdn_chunk_interface.py:53-62).
+def scan_transfers(A, Bm, h0=None):
+    """Second scan level on the GPU: groups g of each sequence map S_in -> A[:, g] @ S_in + Bm[:, g].
 
-    The reference's two-level entry chooses between an approximate "reset" fast path and an exact
-    scan using eps / frac / gt_eps; this implementation is always exact, so those arguments are
-    accepted and ignored.  Returns (out, final_state, info) like the reference; info is an empty
-    fp32 tensor.
+    A, Bm: fp32 [n_seq, G, 128, 128]; h0: fp32 [n_seq, 128, 128] or None.  Returns (s_in, s_final): the state
+    every group starts from, fp32 [n_seq, G, 128, 128], and the state after the last group [n_seq, 128, 128].
     """
-    out, hT = _forward(q, k, v, g, beta, True, None, "auto")
-    return out, hT, torch.empty(0, dtype=torch.float32, device=out.device)
+    n_seq, G = A.shape[:2]
+    A, Bm = A.contiguous(), Bm.contiguous()
+    s_in = torch.empty_like(A)
+    s_final = torch.empty((n_seq, GDN_D, GDN_D), dtype=torch.float32, device=A.device)
+    h = None if h0 is None else h0.to(torch.float32).contiguous()
+    with torch.cuda.device(A.device):
+        st = _lib.load().gdn_chunk_scan_transfers(
+            A.data_ptr(), Bm.data_ptr(), h.data_ptr() if h is not None else None, s_in.data_ptr(),
+            s_final.data_ptr(), n_seq, G, torch.cuda.current_stream(A.device).cuda_stream)
+    _lib.check(st, "gdn_chunk_scan_transfers")
+    return s_in, s_final
+
+
+def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt_eps=1e-2, initial_state=None):
+    """Explicit two-level chunk scan (same name and leading arguments as the reference's
+    gdn_chunk_interface.py:53-62).
+
+    The sequence is cut into groups of `group_chunks` 64-token chunks.  Pass 1 runs every group as an independent
+    sequence twice - from a zero state (giving B_g) and, with zero values, from an identity state (giving A_g) - so
+    that S_out = A_g S_in + B_g; the scan kernel chains these maps in fp32; pass 2 runs every group from its true
+    incoming state and writes the output.  Always exact: eps / frac / gt_eps, which steer the reference's
+    approximate reset path, are accepted and ignored.  Returns (out, final_state, info); info holds the number of
+    groups.  S must be a multiple of 64 * group_chunks (otherwise the serial path is used).
+    """
+    q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+    B, S, Hk, Hv = _check_inputs(q, k, v, g, beta)
+    seg = GDN_CHUNK * int(group_chunks)
+    G = S // seg if seg > 0 else 0
+    if G < 2 or S % seg != 0:
+        out, hT = _forward(q, k, v, g, beta, True, initial_state, "auto")
+        return out, hT, torch.ones(1, dtype=torch.float32, device=out.device)
+    dev = q.device
+
+    def fold(x):      # [B, G*seg, ...] -> [B*G, seg, ...]: every group becomes a batch element
+        return x.reshape(B * G, seg, *x.shape[2:])
+
+    qg, kg, vg, gg, bg = (fold(x) for x in (q, k, v, g, beta))
+    _, Bm = _forward(qg, kg, vg, gg, bg, True, None, "auto")                       # [B*G, Hv, 128, 128]
+    eye = torch.eye(GDN_D, dtype=torch.float32, device=dev).expand(B * G, Hv, GDN_D, GDN_D).contiguous()
+    _, A = _forward(qg, kg, torch.zeros_like(vg), gg, bg, True, eye, "auto")
+    # [B*G, Hv, ...] -> [B*Hv, G, ...]
+    to_seq = lambda x: x.reshape(B, G, Hv, GDN_D, GDN_D).permute(0, 2, 1, 3, 4).reshape(B * Hv, G, GDN_D, GDN_D)
+    h0 = None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32).reshape(B * Hv, GDN_D, GDN_D)
+    s_in, s_final = scan_transfers(to_seq(A), to_seq(Bm), h0)
+    s_in = s_in.reshape(B, Hv, G, GDN_D, GDN_D).permute(0, 2, 1, 3, 4).reshape(B * G, Hv, GDN_D, GDN_D)
+    out, _ = _forward(qg, kg, vg, gg, bg, False, s_in, "auto")
+    info = torch.full((1,), float(G), dtype=torch.float32, device=dev)
+    return out.reshape(B, S, Hv, GDN_D), s_final.reshape(B, Hv, GDN_D, GDN_D), info
 
 
 def gdn_chunk_reference(q, k, v, g, beta, chunk_size=64, mode="chunk"):

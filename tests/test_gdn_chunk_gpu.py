@@ -186,3 +186,38 @@ def test_reference_test_case_vs_recurrent_oracle(S):
     rel = np.abs(out - ro).max() / (np.abs(ro).max() + 1e-9)
     assert rel < 2e-2, f"out rel={rel:.2e}"
     assert_close(st, rs, "state")
+
+
+def test_scan_transfers_kernel_matches_numpy():
+    from gdn_qsa_sm80_b200.gdn_chunk_interface import scan_transfers
+    gen = torch.Generator().manual_seed(4)
+    n_seq, G = 3, 5
+    A = 0.1 * torch.randn(n_seq, G, 128, 128, generator=gen)
+    Bm = torch.randn(n_seq, G, 128, 128, generator=gen)
+    h0 = torch.randn(n_seq, 128, 128, generator=gen)
+    s_in, s_fin = scan_transfers(A.cuda(), Bm.cuda(), h0.cuda())
+    S = h0.double().numpy()
+    for gidx in range(G):
+        assert np.abs(s_in[:, gidx].cpu().numpy() - S).max() < 1e-4
+        S = A[:, gidx].double().numpy() @ S + Bm[:, gidx].double().numpy()
+    assert np.abs(s_fin.cpu().numpy() - S).max() < 1e-4
+
+
+@pytest.mark.parametrize("workload,group_chunks", [("default", 2), ("long_context", 4)])
+def test_twolevel_scan_matches_serial_path_and_oracle(workload, group_chunks):
+    """The explicit two-level scan (groups of chunks, affine transfers, fp32 scan, replay) against the serial
+    path and the oracle; the long_context gates decay slowly, so the transfer matrices are far from zero."""
+    S = 64 * group_chunks * 4
+    q, k, v, g, beta, _ = make_inputs(workload, seed=61, B=2, S=S, Hq=2, Hv=4)
+    h0 = 0.1 * torch.randn(2, 4, 128, 128, generator=torch.Generator().manual_seed(62))
+    dev = "cuda"
+    out, st, info = gdn_chunk_twolevel(q.to(dev), k.to(dev), v.to(dev), g.to(dev), beta.to(dev),
+                                       group_chunks=group_chunks, initial_state=h0.to(dev))
+    check_device_status()
+    assert float(info[0]) == 4.0
+    ro, rs = oracle_f32(q, k, v, g, beta, h0)
+    assert_close(out.float().cpu().numpy(), ro, "two-level out vs oracle")
+    assert_close(st.cpu().numpy(), rs, "two-level state vs oracle")
+    so, ss = run(q, k, v, g, beta, h0, "auto")
+    assert_close(out.float().cpu().numpy(), so, "two-level out vs serial")
+    assert_close(st.cpu().numpy(), ss, "two-level state vs serial")
