@@ -34,6 +34,8 @@ sys.path.insert(0, ROOT)
 METRIC = "gdn_chunk_fwd_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# dram__bytes_read.sum + dram__bytes_write.sum of one gdn_chain_kernel launch on the default workload (ncu, profiles/)
+CHAIN_DRAM_BYTES_DEFAULT = 361.8e6
 
 
 def flops_per_token(Hq, Hv, C=64, D=128):
@@ -268,25 +270,63 @@ def main():
         e2e = {"value": total_tokens / (e2e_ms / n_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "steps": n_e2e}
 
+    # ---- the two kernels of a step timed on their own (CUDA events on the launching stream, L2 flushed) ----
+    per_kernel = None
+    if args.path in ("auto", "twopass_nv32", "twopass_nv64"):
+        per_kernel = {}
+        step()                                            # leaves a valid workspace for the chain-only launches
+        for name in ("prepare_only", "chain_only"):
+            times = []
+            for _ in range(max(3, min(args.steps, 10))):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                gdn_chunk(d_in[0], d_in[1], d_in[2], d_in[3], d_in[4], output_final_state=True,
+                          initial_state=d_in[5], path=name)
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b))
+            per_kernel[name] = statistics.median(times)
+        check_device_status(dev)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # ---- roofline of the dominant (here: the only) kernel, per launch on one GPU ---------------------------
+    # ---- roofline: the whole step, and the dominant kernel (the chain) on its own -------------------------
     peaks, peak_kind = load_peaks()
     tokens_local = B_local * w.S
-    kernel_s = statistics.median(step_ms) * 1e-3
+    step_s = statistics.median(step_ms) * 1e-3
     fl = flops_per_token(w.Hq, w.Hv) * tokens_local
     by = bytes_per_token(w.Hq, w.Hv) * tokens_local + B_local * w.Hv * 65536 * (2 if w.h0 != "zeros" else 1)
-    tf = fl / kernel_s / 1e12
-    roofline = {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                "frac": tf / peaks["bf16_tflops"], "traffic": None,
-                "peak_kind": f"{peak_kind} (burst cuBLAS bf16)",
-                "algorithmic_flops_per_launch": fl,
-                "hbm": {"achieved": by / kernel_s / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                        "frac": by / kernel_s / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes_per_launch": by},
-                "kernel_ms_median": kernel_s * 1e3}
+    whole = {"achieved": fl / step_s / 1e12, "frac": fl / step_s / 1e12 / peaks["bf16_tflops"],
+             "algorithmic_flops_per_step": fl, "step_ms_median": step_s * 1e3,
+             "hbm": {"achieved": by / step_s / 1e9, "frac": by / step_s / 1e9 / peaks["hbm_gbs"],
+                     "algorithmic_bytes_per_step": by, "peak": peaks["hbm_gbs"], "unit": "GB/s"}}
+    if per_kernel:
+        # flops of the chain kernel: W S, Q S, K^T v~ (2 D D each) and P v_new (2 C D) per value head and token;
+        # the prepare kernel has the rest (K K^T, Q K^T per qk head; T K, T V per value head)
+        fl_chain = w.Hv * (6 * 128 * 128 + 2 * 64 * 128) * tokens_local
+        fl_prep = fl - fl_chain
+        k_s = per_kernel["chain_only"] * 1e-3
+        tf = fl_chain / k_s / 1e12
+        # DRAM bytes of one chain launch on the default workload, from an ncu capture (profiles/): read + write
+        traffic = CHAIN_DRAM_BYTES_DEFAULT if (args.workload == "default" and world == 1) else None
+        roofline = {"kernel": "gdn_chain_kernel", "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"],
+                    "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "traffic": traffic,
+                    "peak_kind": f"{peak_kind} (burst cuBLAS bf16)", "algorithmic_flops_per_launch": fl_chain,
+                    "kernel_ms": per_kernel["chain_only"],
+                    "share_of_step": per_kernel["chain_only"] / (per_kernel["chain_only"] + per_kernel["prepare_only"]),
+                    "prepare_kernel": {"kernel_ms": per_kernel["prepare_only"], "algorithmic_flops_per_launch": fl_prep,
+                                       "achieved": fl_prep / (per_kernel["prepare_only"] * 1e-3) / 1e12,
+                                       "frac": fl_prep / (per_kernel["prepare_only"] * 1e-3) / 1e12 / peaks["bf16_tflops"]},
+                    "whole_step": whole}
+    else:
+        roofline = {"kernel": "whole step", "bound": "tensor", "achieved": whole["achieved"], "peak": peaks["bf16_tflops"],
+                    "unit": "TFLOP/s", "frac": whole["frac"], "traffic": None,
+                    "peak_kind": f"{peak_kind} (burst cuBLAS bf16)", "algorithmic_flops_per_launch": fl,
+                    "whole_step": whole}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks.summary(),

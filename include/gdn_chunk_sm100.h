@@ -37,6 +37,9 @@ extern "C" {
 #define GDN_PATH_FUSED_NV32 3    /* single fused tcgen05 kernel, 32 value columns per CTA            */
 #define GDN_PATH_TWOPASS_NV64 4  /* prepare kernel + chain kernel, 64 value columns per chain CTA    */
 #define GDN_PATH_TWOPASS_NV32 5  /* prepare kernel + chain kernel, 32 value columns per chain CTA    */
+#define GDN_PATH_PREPARE_ONLY 6  /* measurement aid: only the prepare kernel (fills the workspace)    */
+#define GDN_PATH_CHAIN_ONLY 7    /* measurement aid: only the chain kernel, on the workspace an earlier
+                                    call with the same arguments and scratch left behind              */
 
 #define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
 #define GDN_CHUNK 64             /* tokens per chunk                                                */
