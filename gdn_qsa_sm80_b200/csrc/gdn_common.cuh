@@ -39,7 +39,7 @@ struct Workspace {
 
 // Byte offsets of the workspace arrays inside the scratch buffer (the status word sits at offset 0).
 struct WorkspaceLayout {
-    size_t W, P, U, vec, total;
+    size_t W, P, U, vec, flags, flag_bytes, total;
 };
 inline WorkspaceLayout workspace_layout(size_t tiles) {
     WorkspaceLayout l;
@@ -47,7 +47,9 @@ inline WorkspaceLayout workspace_layout(size_t tiles) {
     l.P = l.W + tiles * 16384;
     l.U = l.P + tiles * 8192;
     l.vec = l.U + tiles * 32768;
-    l.total = l.vec + tiles * 1024;
+    l.flags = l.vec + tiles * 1024;                      // one int per tile: "prepared" flags of the single-launch path
+    l.flag_bytes = (tiles * 4 + 1023) / 1024 * 1024;
+    l.total = l.flags + l.flag_bytes;
     return l;
 }
 
@@ -67,6 +69,10 @@ int launch_fused(const Problem& p, int nv, cudaStream_t stream);
 // state recurrence plus outputs, reading the workspace).  Both return a GDN_* status.
 int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream);
 int launch_chain(const Problem& p, const Workspace& ws, int nv, cudaStream_t stream);
+// Single-launch variant (prepare shared among the four column CTAs of a head, chain in the same kernel);
+// only when all CTAs fit on the GPU at once.
+bool coop_supported(const Problem& p);
+int launch_coop(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream);
 
 // Host helper: encode a tiled TMA descriptor for a row-major tensor of `rank` dims
 // (dims/strides innermost first; strides in bytes for dims 1..rank-1).  swizzle_bytes: 128 or 64.

@@ -24,6 +24,18 @@ struct PrepScratch {
     float wsum[2];
 };
 
+// Which 128 threads run the prepare steps: the whole CTA (thread index = threadIdx.x, __syncthreads) or a
+// 128-thread group inside a larger CTA (its own thread numbering and a named barrier).
+struct PrepCtx {
+    int tid;
+    int bar;   // 0 = __syncthreads(), otherwise the id of a 128-thread named barrier
+    __device__ __forceinline__ static PrepCtx whole_cta() { return PrepCtx{static_cast<int>(threadIdx.x), 0}; }
+    __device__ __forceinline__ void sync() const {
+        if (bar == 0) __syncthreads();
+        else named_bar_sync(static_cast<uint32_t>(bar), 128);
+    }
+};
+
 template <bool GATE_F32>
 __device__ __forceinline__ float prep_load_gate(const void* p, size_t idx) {
     if (GATE_F32) return static_cast<const float*>(p)[idx];
@@ -33,8 +45,9 @@ __device__ __forceinline__ float prep_load_gate(const void* p, size_t idx) {
 // Loads the log gate and the update gate of token `tid` of a chunk (threads 0-63; zeros for padding).
 template <bool GATE_F32>
 __device__ __forceinline__ void prep_load_gates(const void* g, const void* beta, size_t tok0, int hv, int Hv,
-                                                int valid, float& gv, float& bv) {
-    const int tid = threadIdx.x;
+                                                int valid, float& gv, float& bv,
+                                                PrepCtx ctx = PrepCtx::whole_cta()) {
+    const int tid = ctx.tid;
     gv = 0.f;
     bv = 0.f;
     if (tid < valid) {
@@ -45,11 +58,12 @@ __device__ __forceinline__ void prep_load_gates(const void* g, const void* beta,
 }
 
 // Gate cumsum over the chunk by warp shuffles (threads 0-63 hold one token each: gv, bv) and the decay tables.
-// Contains two __syncthreads(); a third one is needed before the tables are read.
+// Contains two barriers of the group; a third one is needed before the tables are read.
 // If vec_out != nullptr, also writes the per-token factors a later kernel needs:
 //   vec_out[i] = exp(gamma_C - gamma_i), vec_out[64+i] = scale * exp(gamma_i), vec_out[128] = exp(gamma_C).
-__device__ __forceinline__ void prep_gates(PrepScratch& ps, float gv, float bv, float scale, float* vec_out) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+__device__ __forceinline__ void prep_gates(PrepScratch& ps, float gv, float bv, float scale, float* vec_out,
+                                           PrepCtx ctx = PrepCtx::whole_cta()) {
+    const int tid = ctx.tid, warp = tid >> 5, lane = tid & 31;
     float gsum = 0.f;
     if (tid < kChunk) {
         gsum = gv;
@@ -60,13 +74,13 @@ __device__ __forceinline__ void prep_gates(PrepScratch& ps, float gv, float bv, 
         }
         if (lane == 31) ps.wsum[warp] = gsum;
     }
-    __syncthreads();
+    ctx.sync();
     if (tid < kChunk) {
         if (warp == 1) gsum += ps.wsum[0];
         ps.gam[tid] = gsum * kLog2e;
         ps.bet[tid] = bv;
     }
-    __syncthreads();
+    ctx.sync();
     if (tid < kChunk) {
         const float gi = ps.gam[tid], gC = ps.gam[kChunk - 1];
         const float e = exp2f(gi);
@@ -159,9 +173,10 @@ __device__ __forceinline__ void store_c_frag(float* m, int ld, int lane, const f
 // `Yt` is a scratch of at least 32*kY2Stride floats.  Blocked inversion:
 //   16x16 diagonal blocks by forward substitution in fp32 registers, then
 //   [[L11,0],[L21,L22]]^-1 = [[X11,0],[-X22 L21 X11, X22]] at block sizes 16 and 32 with TF32 warp MMAs.
-// Contains its own __syncthreads(); `As` and `Tm` must be complete before the call (one barrier before).
-__device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* Tm, float* Yt) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+// Contains its own barriers; `As` and `Tm` must be complete before the call (one barrier before).
+__device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* Tm, float* Yt,
+                                                       PrepCtx ctx = PrepCtx::whole_cta()) {
+    const int tid = ctx.tid, warp = tid >> 5, lane = tid & 31;
     if (tid < 64) {
         const int blk = tid >> 4, c = tid & 15;
         const float* a = As + (16 * blk) * kSolveStride + 16 * blk;
@@ -189,7 +204,7 @@ __device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* T
 #pragma unroll
         for (int i = 0; i < 16; ++i) Tm[(16 * blk + i) * kSolveStride + 16 * blk + c] = x[i];
     }
-    __syncthreads();
+    ctx.sync();
     {   // level 1: pairs of 16-blocks.  warp -> (pair p, 8-column tile nt)
         const int p = warp >> 1, nt = warp & 1;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -201,7 +216,7 @@ __device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* T
             mma_tf32_16x8x8(acc, a, b);
         }
         store_c_frag(Yt + (16 * p) * kY1Stride + 8 * nt, kY1Stride, lane, acc, 1.f);
-        __syncthreads();
+        ctx.sync();
         float acc2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
@@ -212,7 +227,7 @@ __device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* T
         }
         store_c_frag(Tm + (32 * p + 16) * kSolveStride + 32 * p + 8 * nt, kSolveStride, lane, acc2, -1.f);
     }
-    __syncthreads();
+    ctx.sync();
     {   // level 2: the 32x32 lower-left block.  warp -> (16-row block rb, 16-column block cb)
         const int rb = warp >> 1, cb = warp & 1;
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -230,7 +245,7 @@ __device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* T
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
             store_c_frag(Yt + (16 * rb) * kY2Stride + 16 * cb + 8 * nt, kY2Stride, lane, acc[nt], 1.f);
-        __syncthreads();
+        ctx.sync();
         float acc2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
@@ -247,13 +262,13 @@ __device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* T
         for (int nt = 0; nt < 2; ++nt)
             store_c_frag(Tm + (32 + 16 * rb) * kSolveStride + 16 * cb + 8 * nt, kSolveStride, lane, acc2[nt], -1.f);
     }
-    __syncthreads();
+    ctx.sync();
 }
 
 // Zeroes the six 16x16 blocks of `Tm` above the block diagonal (all 128 threads; what prep_invert_unit_lower
 // expects on entry).
-__device__ __forceinline__ void prep_zero_upper_blocks(float* Tm) {
-    const int tid = threadIdx.x;
+__device__ __forceinline__ void prep_zero_upper_blocks(float* Tm, PrepCtx ctx = PrepCtx::whole_cta()) {
+    const int tid = ctx.tid;
 #pragma unroll
     for (int e = 0; e < 3; ++e) {
         const int idx = tid + 128 * e;              // 384 float4 = 6 blocks x 16 rows x 4 float4

@@ -40,6 +40,8 @@ extern "C" {
 #define GDN_PATH_PREPARE_ONLY 6  /* measurement aid: only the prepare kernel (fills the workspace)    */
 #define GDN_PATH_CHAIN_ONLY 7    /* measurement aid: only the chain kernel, on the workspace an earlier
                                     call with the same arguments and scratch left behind              */
+#define GDN_PATH_COOP 8          /* one launch: the four 32-column CTAs of a head share the prepare work
+                                    through the workspace while their chains run; needs 4*B*Hv <= #SMs    */
 
 #define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
 #define GDN_CHUNK 64             /* tokens per chunk                                                */
