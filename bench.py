@@ -36,6 +36,7 @@ UNIT = "tokens/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one gdn_chain_kernel launch on the default workload (ncu, profiles/)
 CHAIN_DRAM_BYTES_DEFAULT = 361.8e6
+COOP_DRAM_BYTES_DEFAULT = None   # filled from the ncu capture of gdn_coop_kernel (profiles/)
 
 
 def flops_per_token(Hq, Hv, C=64, D=128):
@@ -273,7 +274,12 @@ def main():
 
     # ---- the two kernels of a step timed on their own (CUDA events on the launching stream, L2 flushed) ----
     per_kernel = None
-    if args.path in ("auto", "twopass_nv32", "twopass_nv64"):
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    single_launch = args.path == "coop" or (args.path == "auto" and 4 * B_local * w.Hv <= n_sm)
+    cfg["kernels"] = ("gdn_coop_kernel (one launch)" if single_launch else
+                      "gdn_prepare_kernel + gdn_chain_kernel" if args.path in ("auto", "twopass_nv32", "twopass_nv64")
+                      else args.path)
+    if args.path in ("auto", "twopass_nv32", "twopass_nv64") and not single_launch:
         per_kernel = {}
         step()                                            # leaves a valid workspace for the chain-only launches
         for name in ("prepare_only", "chain_only"):
@@ -323,6 +329,13 @@ def main():
                                        "achieved": fl_prep / (per_kernel["prepare_only"] * 1e-3) / 1e12,
                                        "frac": fl_prep / (per_kernel["prepare_only"] * 1e-3) / 1e12 / peaks["bf16_tflops"]},
                     "whole_step": whole}
+    elif single_launch:
+        # one kernel per step: its duration is the step's (CUDA events around the launch)
+        traffic = COOP_DRAM_BYTES_DEFAULT if (args.workload == "default" and world == 1) else None
+        roofline = {"kernel": "gdn_coop_kernel", "bound": "tensor", "achieved": whole["achieved"], "peak": peaks["bf16_tflops"],
+                    "unit": "TFLOP/s", "frac": whole["frac"], "traffic": traffic,
+                    "peak_kind": f"{peak_kind} (burst cuBLAS bf16)", "algorithmic_flops_per_launch": fl,
+                    "kernel_ms": step_s * 1e3, "share_of_step": 1.0, "whole_step": whole}
     else:
         roofline = {"kernel": "whole step", "bound": "tensor", "achieved": whole["achieved"], "peak": peaks["bf16_tflops"],
                     "unit": "TFLOP/s", "frac": whole["frac"], "traffic": None,

@@ -69,7 +69,7 @@ int encode_qkv_maps(const Problem& p, void* tq, void* tk, void* tv, int v_box_co
     return 0;
 }
 
-int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu) {
+int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu_store, void* tu_load, int nv) {
     const int NT = (p.S + kChunk - 1) / kChunk;
     const unsigned long long rows = static_cast<unsigned long long>(p.B) * p.Hv * NT * kChunk;
     {
@@ -83,9 +83,11 @@ int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void*
         if (encode_tma(tp, ws.P, 2, 2, d, s, box, 128)) return 1;
     }
     {
-        const unsigned long long d[2] = {128, rows}, s[1] = {512};
-        const unsigned box[2] = {32, 64};
-        if (encode_tma(tu, ws.U, 4, 2, d, s, box, 128)) return 1;
+        const unsigned long long d[2] = {128, rows}, s[1] = {256};
+        const unsigned box[2] = {64, 64};
+        if (tu_store && encode_tma(tu_store, ws.U, 2, 2, d, s, box, 128)) return 1;
+        const unsigned boxl[2] = {static_cast<unsigned>(nv), 64};
+        if (tu_load && encode_tma(tu_load, ws.U, 2, 2, d, s, boxl, nv * 2)) return 1;
     }
     return 0;
 }
@@ -187,9 +189,10 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
     Workspace ws;
     ws.W = reinterpret_cast<__nv_bfloat16*>(base + l.W);
     ws.P = reinterpret_cast<__nv_bfloat16*>(base + l.P);
-    ws.U = reinterpret_cast<float*>(base + l.U);
+    ws.U = reinterpret_cast<__nv_bfloat16*>(base + l.U);
     ws.vec = reinterpret_cast<float*>(base + l.vec);
-    if (path == GDN_PATH_COOP)
+    // few independent sequences: one launch in which a head's four column CTAs share the prepare work
+    if (path == GDN_PATH_COOP || (path == GDN_PATH_AUTO && coop_supported(p)))
         return launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream);
     if (path == GDN_PATH_CHAIN_ONLY) return launch_chain(p, ws, nv, stream);   // workspace left by an earlier call
     const int st = launch_prepare(p, ws, stream);
@@ -234,7 +237,7 @@ const char* gdn_chunk_error_string(int status) {
 // by every call, everything else is fully rewritten before it is read, and two calls that overlap on
 // the GPU (different streams) would race on it.
 // ---------------------------------------------------------------------------------------------
-constexpr size_t kNoAllocBytes = 16u << 20;   // 16 MiB: up to 287 (batch x value head x 64-token chunk) tiles
+constexpr size_t kNoAllocBytes = 16u << 20;   // 16 MiB: up to 399 (batch x value head x 64-token chunk) tiles
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 static void* g_noalloc_addr[64] = {nullptr};
 static std::mutex g_noalloc_mutex;

@@ -38,10 +38,10 @@ struct CSmem {
     static constexpr uint32_t KT = 0;                       // K: 2 dk-halves x 64 rows x 128 B
     static constexpr uint32_t QW = KT + 16384;              // [Q;W]: 2 k-halves x 128 rows x 128 B
     static constexpr uint32_t PB = QW + 32768;              // P: 64 rows x 128 B; the 64 rows after it are don't-care
-    static constexpr uint32_t UB = PB + 8192;               // U slice fp32: NV/32 groups x 64 rows x 128 B
-    static constexpr uint32_t VEC = UB + 64 * NV * 4;       // 256 floats
+    static constexpr uint32_t UB = PB + 8192;               // U slice bf16: 64 rows x kRowBytes
+    static constexpr uint32_t VEC = UB + 64 * NV * 2;       // 256 floats
     static constexpr uint32_t kStage = VEC + 1024;
-    static constexpr uint32_t kStageTx = 16384 + 16384 + 16384 + 8192 + 64 * NV * 4 + 1024;
+    static constexpr uint32_t kStageTx = 16384 + 16384 + 16384 + 8192 + 64 * NV * 2 + 1024;
     // after the ring
     static constexpr uint32_t VN = STAGES * kStage;         // v_new  bf16 64 rows x kRowBytes
     static constexpr uint32_t VS = VN + 64 * kRowBytes;     // v~
@@ -49,7 +49,9 @@ struct CSmem {
     static constexpr uint32_t kBytes = SB + 128 * kRowBytes;
     static constexpr uint32_t kDynamic = kBytes + 1024;
     static_assert(kStage % 1024 == 0 && VN % 1024 == 0, "tiles must stay 1024-byte aligned");
-    static_assert(UB - PB == 8192 && 64 * NV * 4 >= 8192, "the don't-care rows of the P operand must lie inside the stage");
+    // the 64 don't-care rows of the P operand (8 KB after PB) run into U, the factors and whatever follows the stage:
+    // always inside the allocation, because VN/VS/SB follow the last stage
+    static_assert(UB - PB == 8192, "P tile is 8 KB");
 };
 
 constexpr int kDevTimeoutChainFull = 0x201;
@@ -146,9 +148,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 tma_load_2d(st + L::QW + 8192, &tm_w, &bar_full[s], 0, row0);
                 tma_load_2d(st + L::QW + 24576, &tm_w, &bar_full[s], 64, row0);
                 tma_load_2d(st + L::PB, &tm_p, &bar_full[s], 0, row0);
-#pragma unroll
-                for (int gq = 0; gq < NV / 32; ++gq)
-                    tma_load_2d(st + L::UB + gq * 8192, &tm_u, &bar_full[s], dv0 + gq * 32, row0);
+                tma_load_2d(st + L::UB, &tm_u, &bar_full[s], dv0, row0);
                 bulk_load_1d(st + L::VEC, ws.vec + (tile0 + t) * 256, 1024, &bar_full[s]);
             }
         }
@@ -269,9 +269,14 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + part * 32), w);
                     float u[32];
 #pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) {
-                        const float4 uv = *reinterpret_cast<const float4*>(stg + L::UB + part * 8192 + swz_chunk_offset<128>(i, ch));
-                        u[4 * ch] = uv.x; u[4 * ch + 1] = uv.y; u[4 * ch + 2] = uv.z; u[4 * ch + 3] = uv.w;
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const uint4 uv = *reinterpret_cast<const uint4*>(stg + L::UB + swz_chunk_offset<NV * 2>(i, part * 4 + ch));
+                        const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {     // bf16 pair -> two fp32
+                            u[8 * ch + 2 * e] = __uint_as_float(uw[e] << 16);
+                            u[8 * ch + 2 * e + 1] = __uint_as_float(uw[e] & 0xffff0000u);
+                        }
                     }
                     tmem_ld_wait();
 #pragma unroll
@@ -365,7 +370,7 @@ template <int NV, int STAGES>
 int launch_chain_nv(const Problem& p, const Workspace& ws, cudaStream_t stream) {
     alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
-    if (encode_workspace_maps(p, ws, &tw, &tp, &tu)) return GDN_ERR_DRIVER;
+    if (encode_workspace_maps(p, ws, &tw, &tp, nullptr, &tu, NV)) return GDN_ERR_DRIVER;
     using L = CSmem<NV, STAGES>;
     auto kernel = gdn_chain_kernel<NV, STAGES>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess)

@@ -30,8 +30,8 @@ constexpr int STAGES = 2;
 struct XSmem {
     static constexpr uint32_t kRowBytes = NV * 2;
     // chain ring, one stage:
-    static constexpr uint32_t KT = 0, QW = 16384, PB = 49152, UB = 57344, VEC = 65536, kStage = 66560;
-    static constexpr uint32_t kStageTx = 16384 + 16384 + 16384 + 8192 + 8192 + 1024;
+    static constexpr uint32_t KT = 0, QW = 16384, PB = 49152, UB = 57344, VEC = 61440, kStage = 62464;
+    static constexpr uint32_t kStageTx = 16384 + 16384 + 16384 + 8192 + 4096 + 1024;
     static constexpr uint32_t VN = STAGES * kStage;      // v_new bf16, 64 rows x 64 B
     static constexpr uint32_t VS = VN + 4096;            // decay-scaled v_new
     static constexpr uint32_t SB = VS + 4096;            // bf16 state, 128 rows x 64 B
@@ -136,13 +136,7 @@ __device__ __forceinline__ void coop_prepare_role(uint8_t* sm, uint32_t sm_u32, 
     uint32_t ph_free = 0;
     for (; t < NT; t += 4) {
         const size_t tile = tile0 + t;
-        if (ptid == 0 && t != split) {   // the previous tile's staging tiles have been read by its TMA stores
-            mbar_wait_abortable(bar_free, ph_free, p.status, kTimeoutPrepTma, abortp);
-            ph_free ^= 1;
-            issue_kq(t);
-        }
         prep_gates(ps, gv, bv, scale, ws.vec + tile * 256, ctx);
-        prep_zero_upper_blocks(Tm, ctx);
         ctx.sync();
         GDN_PHASE(0)
         mbar_wait_abortable(bar_ptma, ph_tma, p.status, kTimeoutPrepTma, abortp);
@@ -167,6 +161,11 @@ __device__ __forceinline__ void coop_prepare_role(uint8_t* sm, uint32_t sm_u32, 
             tma_load_4d(kq + 8192, tm_v, bar_ptma, 0, hv, t * kChunk, b);
             tma_load_4d(kq + 24576, tm_v, bar_ptma, 64, hv, t * kChunk, b);
         }
+        if (t != split) {   // the previous tile's W / U staging tiles (the A and T buffers) have been read by its TMA stores
+            mbar_wait_abortable(bar_free, ph_free, p.status, kTimeoutPrepTma, abortp);
+            ph_free ^= 1;
+        }
+        prep_zero_upper_blocks(Tm, ctx);
         {
             float ri, diag[16];
             prep_row_setup(ps, i, ri, diag);
@@ -243,8 +242,11 @@ __device__ __forceinline__ void coop_prepare_role(uint8_t* sm, uint32_t sm_u32, 
         ph_mma ^= 1;
         tc_fence_after_sync();
         GDN_PHASE(6)
-        // W (bf16) and U (fp32) leave through swizzled staging tiles and TMA stores: W in the Q/V slots of the
-        // [K;Q] buffer, U across the A/T matrices (all dead once the last UMMA of the tile has finished)
+        // the tile's K/Q/V buffer is free: next tile's K and Q
+        const int tn = t + 4;
+        if (tn < NT && ptid == 0) issue_kq(tn);
+        // W and U (bf16) leave through swizzled staging tiles and TMA stores: W in the A buffer, U in the T buffer
+        // (both dead once the last UMMA of the tile has finished)
         {
             uint32_t r[32];
             if (pwarp < 2) {
@@ -259,7 +261,7 @@ __device__ __forceinline__ void coop_prepare_role(uint8_t* sm, uint32_t sm_u32, 
                         pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
                         pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
                         pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-                        *reinterpret_cast<uint4*>(kq + 8192 + (q4 >> 1) * 16384 + swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
+                        *reinterpret_cast<uint4*>(sm + XSmem::PAS + (q4 >> 1) * 8192 + swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
                     }
                 }
             } else {
@@ -268,9 +270,14 @@ __device__ __forceinline__ void coop_prepare_role(uint8_t* sm, uint32_t sm_u32, 
                     tmem_ld_x32(tmem_addr(tm_prep, lane_base, 128 + q4 * 32), r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4*>(sm + XSmem::PAS + q4 * 8192 + swz_chunk_offset<128>(i, c)) =
-                            make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint4 pk;
+                        pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                        pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                        pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                        pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                        *reinterpret_cast<uint4*>(sm + XSmem::PTM + (q4 >> 1) * 8192 + swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
+                    }
                 }
             }
         }
@@ -279,7 +286,6 @@ __device__ __forceinline__ void coop_prepare_role(uint8_t* sm, uint32_t sm_u32, 
         ctx.sync();
         // hand the staging tiles to the publisher thread (warp 6): it stores them, frees them and raises the flag
         if (ptid == 0) mbar_arrive(bar_ready);
-        const int tn = t + 4;
         if (tn < NT)
             prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(b) * p.S + tn * kChunk, hv, p.Hv,
                                       min(kChunk, p.S - tn * kChunk), gv, bv, ctx);
@@ -297,7 +303,8 @@ template <bool GATE_F32>
 __global__ void __launch_bounds__(384, 1)
 gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
-                const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_u, Problem p, Workspace ws,
+                const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_u,
+                const __grid_constant__ CUtensorMap tm_us, Problem p, Workspace ws,
                 int* flags) {
     using L = XSmem;
     extern __shared__ uint8_t smem_raw[];
@@ -383,11 +390,10 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 ph ^= 1;
                 const size_t tile = tile0 + t;
                 const int row0 = static_cast<int>(tile * kChunk);
-                uint8_t* kq = sm + L::PKQ;
-                tma_store_2d(&tm_w, kq + 8192, 0, row0);
-                tma_store_2d(&tm_w, kq + 24576, 64, row0);
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) tma_store_2d(&tm_u, sm + L::PAS + q4 * 8192, q4 * 32, row0);
+                tma_store_2d(&tm_w, sm + L::PAS, 0, row0);
+                tma_store_2d(&tm_w, sm + L::PAS + 8192, 64, row0);
+                tma_store_2d(&tm_us, sm + L::PTM, 0, row0);
+                tma_store_2d(&tm_us, sm + L::PTM + 8192, 64, row0);
                 tma_store_commit();
                 tma_store_wait_read();
                 mbar_arrive(&bar_free);
@@ -470,25 +476,41 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
         };
 
+        const bool cprof = p.prof != nullptr && issuer && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        long long cacc[7] = {0, 0, 0, 0, 0, 0, 0};
+        long long ct = 0;
+#define GDN_CPHASE(n)                                  \
+    if (cprof) {                                       \
+        const long long now_ = clock64();              \
+        cacc[n] += now_ - ct;                          \
+        ct = now_;                                     \
+    }
         bool ok = mbar_wait_abortable(&bar_full[0], 0, p.status, kTimeoutFull, abortp);
         if (ok) load_factors(0);
         tc_fence_before_sync();
         named_bar_sync(2, 128);
         if (issuer && ok) issue_d3(0);
 
+        if (cprof) ct = clock64();
         for (int t = 0; t < NT; ++t) {
             const int s = t % STAGES;
             uint8_t* stg = sm + s * L::kStage;
             if (warp >= 2) {
                 ok = mbar_wait_abortable(&bar_d3, t & 1, p.status, kTimeoutD3, abortp) && ok;
                 tc_fence_after_sync();
+                GDN_CPHASE(0)
                 uint32_t w[32];
                 float x[NV], y[NV], u[32];
                 tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV), w);
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    const float4 uv = *reinterpret_cast<const float4*>(stg + L::UB + swz_chunk_offset<128>(i, ch));
-                    u[4 * ch] = uv.x; u[4 * ch + 1] = uv.y; u[4 * ch + 2] = uv.z; u[4 * ch + 3] = uv.w;
+                for (int ch = 0; ch < 4; ++ch) {
+                    const uint4 uv = *reinterpret_cast<const uint4*>(stg + L::UB + swz_chunk_offset<64>(i, ch));
+                    const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {     // bf16 pair -> two fp32
+                        u[8 * ch + 2 * e] = __uint_as_float(uw[e] << 16);
+                        u[8 * ch + 2 * e + 1] = __uint_as_float(uw[e] & 0xffff0000u);
+                    }
                 }
                 tmem_ld_wait();
 #pragma unroll
@@ -504,6 +526,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
                 named_bar_sync(1, 64);
+                GDN_CPHASE(1)
                 if (issuer && ok) {
                     constexpr uint32_t idesc_kv = umma_idesc_bf16(128, NV, MAJOR_MN, MAJOR_MN);
                     const uint64_t k0 = umma_smem_desc(sm_u32 + s * L::kStage + L::KT, 8192, 1024, SWZ_128B);
@@ -515,6 +538,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     umma_commit(&bar_kv);
                     mbar_arrive(&bar_vn);
                 }
+                GDN_CPHASE(2)
             } else if (t > 0) {
                 ok = mbar_wait_abortable(&bar_pv[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, kTimeoutPV, abortp) && ok;
                 tc_fence_after_sync();
@@ -523,6 +547,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = mbar_wait_abortable(&bar_kv, t & 1, p.status, kTimeoutKV, abortp) && ok;
             tc_fence_after_sync();
             if (tid == 0 && ok) mbar_arrive(&bar_empty[s]);
+            GDN_CPHASE(3)
             {
                 uint32_t r[32];
                 tmem_ld_x32(tmem_addr(tmem, lane_base, kColKV), r);
@@ -532,6 +557,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 store_row32_bf16(sm + L::SB, tid, st);
             }
             fence_proxy_async_smem();
+            GDN_CPHASE(4)
             if (t + 1 < NT) {
                 ok = mbar_wait_abortable(&bar_full[(t + 1) % STAGES], ((t + 1) / STAGES) & 1, p.status, kTimeoutFull, abortp) && ok;
                 if (ok) load_factors(t + 1);
@@ -541,8 +567,13 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             tc_fence_before_sync();
             named_bar_sync(2, 128);
+            GDN_CPHASE(5)
             if (issuer && ok && t + 1 < NT) issue_d3(t + 1);
+            GDN_CPHASE(6)
         }
+#undef GDN_CPHASE
+        if (cprof)
+            for (int n = 0; n < 7; ++n) p.prof[8 + n] = cacc[n];
         if (warp < 2 && NT > 0) {
             ok = mbar_wait_abortable(&bar_pv[(NT - 1) & 1], ((NT - 1) >> 1) & 1, p.status, kTimeoutPV, abortp) && ok;
             tc_fence_after_sync();
@@ -572,15 +603,15 @@ bool coop_supported(const Problem& p) {
 
 int launch_coop(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream) {
     if (!coop_supported(p)) return GDN_ERR_BAD_ARGUMENT;
-    alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu;
+    alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu, tus;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
-    if (encode_workspace_maps(p, ws, &tw, &tp, &tu)) return GDN_ERR_DRIVER;
+    if (encode_workspace_maps(p, ws, &tw, &tp, &tus, &tu, NV)) return GDN_ERR_DRIVER;
     if (cudaMemsetAsync(flags, 0, flag_bytes, stream) != cudaSuccess) return GDN_ERR_CUDA;
     auto go = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XSmem::kDynamic) != cudaSuccess)
             return GDN_ERR_CUDA;
         const dim3 grid(kD / NV, p.Hv, p.B), block(384);
-        kernel<<<grid, block, XSmem::kDynamic, stream>>>(tq, tk, tv, tw, tp, tu, p, ws, flags);
+        kernel<<<grid, block, XSmem::kDynamic, stream>>>(tq, tk, tv, tw, tp, tu, tus, p, ws, flags);
         count_launch();
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };

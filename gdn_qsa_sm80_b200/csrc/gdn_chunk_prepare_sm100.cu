@@ -8,7 +8,7 @@
 //   P     = tril(scale * exp(gamma_i - gamma_j) * Q K^T)          ("intra_chunk_attn")  -> P    [64][64]  bf16
 //   T     = (I + tril(beta_i exp(gamma_i - gamma_j) K K^T, -1))^-1
 //   W     = T (beta e^gamma K)                                   ("k_cumdecay")        -> W    [64][128] bf16
-//   U     = T (beta V)                                           ("new_values")        -> U    [64][128] fp32
+//   U     = T (beta V)                                           ("new_values")        -> U    [64][128] bf16
 // K K^T, Q K^T, T [beta e^gamma K | beta V] run on tcgen05 with TMA-staged tiles; the decay mask is
 // applied in fp32 while the raw products move from TMEM to registers.  The reference computes the
 // same quantities in gdn_prepare_kernel (csrc/gdn_chunk/gdn_kernel.cu:343-710) at chunk 16 with the
@@ -240,7 +240,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                                       min(kChunk, p.S - nxt.s0), gv, bv);
         }
 
-        // epilogue: W (bf16) and U (fp32) into swizzled staging tiles, then TMA stores to the workspace
+        // epilogue: W and U (bf16) into swizzled staging tiles, then TMA stores to the workspace
         tc_fence_after_sync();
         {
             uint32_t r[32];
@@ -266,9 +266,15 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     tmem_ld_x32(tmem_addr(tmem, lane_base, 128 + q4 * 32), r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4*>(sm + PSmem::AS + q4 * 8192 + swz_chunk_offset<128>(i, c)) =
-                            make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint4 pk;
+                        pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                        pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                        pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                        pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                        *reinterpret_cast<uint4*>(sm + PSmem::AS + (q4 >> 1) * 8192 +
+                                                  swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
+                    }
                 }
             }
         }
@@ -280,7 +286,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             tma_store_2d(&tm_w, sm + PSmem::TS, 0, row0);
             tma_store_2d(&tm_w, sm + PSmem::TS + 8192, 64, row0);
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) tma_store_2d(&tm_u, sm + PSmem::AS + q4 * 8192, q4 * 32, row0);
+            for (int h2 = 0; h2 < 2; ++h2) tma_store_2d(&tm_u, sm + PSmem::AS + h2 * 8192, h2 * 64, row0);
             tma_store_commit();
         }
         GDN_PHASE(7)
@@ -303,7 +309,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream) {
     alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
-    if (encode_workspace_maps(p, ws, &tw, &tp, &tu)) return GDN_ERR_DRIVER;
+    if (encode_workspace_maps(p, ws, &tw, &tp, &tu, nullptr, 64)) return GDN_ERR_DRIVER;
     const int NT = (p.S + kChunk - 1) / kChunk;
     const long long tiles = static_cast<long long>(p.B) * p.Hv * NT;
     const long long max_ctas = 2ll * sm_count();

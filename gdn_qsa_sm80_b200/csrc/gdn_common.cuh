@@ -33,7 +33,7 @@ struct Problem {
 struct Workspace {
     __nv_bfloat16* W;   // [tiles][64][128]  W = T (beta e^gamma K)
     __nv_bfloat16* P;   // [tiles][64][64]   masked, scaled Q K^T
-    float* U;           // [tiles][64][128]  U = T (beta V)
+    __nv_bfloat16* U;   // [tiles][64][128]  U = T (beta V)
     float* vec;         // [tiles][256]      exp(gamma_C-gamma_i) | scale exp(gamma_i) | exp(gamma_C) | pad
 };
 
@@ -46,7 +46,7 @@ inline WorkspaceLayout workspace_layout(size_t tiles) {
     l.W = 1024;
     l.P = l.W + tiles * 16384;
     l.U = l.P + tiles * 8192;
-    l.vec = l.U + tiles * 32768;
+    l.vec = l.U + tiles * 16384;
     l.flags = l.vec + tiles * 1024;                      // one int per tile: "prepared" flags of the single-launch path
     l.flag_bytes = (tiles * 4 + 1023) / 1024 * 1024;
     l.total = l.flags + l.flag_bytes;
@@ -83,8 +83,10 @@ inline int encode_tma_bf16(void* tmap_out, const void* base, int rank, const uns
                            const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes) {
     return encode_tma(tmap_out, base, 2, rank, dims, strides_bytes, box, swizzle_bytes);
 }
-// TMA descriptors of the workspace arrays W (bf16, 64x64 boxes), P (bf16, 64x64) and U (fp32, 32x64 boxes).
-int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu);
+// TMA descriptors of the workspace arrays: W, P and U as 64x64 bf16 boxes (128-byte swizzle; what the prepare side
+// stores and the chain side loads for W and P), and U as nv x 64 boxes (swizzle span 2*nv bytes) for the chain's
+// column slice.  tu_load may be null.
+int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu_store, void* tu_load, int nv);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 // TMA descriptors of q, k ([B,S,Hq,128], 64x64 boxes) and v ([B,S,Hv,128], v_box_cols x 64 boxes).

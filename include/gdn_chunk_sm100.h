@@ -31,7 +31,7 @@ extern "C" {
 #define GDN_GATE_F32 1
 
 /* execution path */
-#define GDN_PATH_AUTO 0          /* prepare + chain kernels, column split chosen from B*Hv             */
+#define GDN_PATH_AUTO 0          /* COOP when 4*B*Hv <= #SMs, else prepare + chain kernels (split by B*Hv) */
 #define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
 #define GDN_PATH_FUSED_NV64 2    /* single fused tcgen05 kernel, 64 value columns per CTA            */
 #define GDN_PATH_FUSED_NV32 3    /* single fused tcgen05 kernel, 32 value columns per CTA            */
@@ -57,7 +57,7 @@ size_t gdn_chunk_scratch_bytes(int B, int S, int Hq, int Hv, int path);
 /*
  * Byte offsets, inside the scratch buffer, of the per-chunk arrays the prepare kernel writes and the
  * chain kernel reads (paths AUTO and TWOPASS_*): offsets[0] W bf16 [tiles][64][128], [1] P bf16
- * [tiles][64][64], [2] U fp32 [tiles][64][128], [3] per-token factors fp32 [tiles][256], [4] total
+ * [tiles][64][64], [2] U bf16 [tiles][64][128], [3] per-token factors fp32 [tiles][256], [4] total
  * bytes; tile = (b*Hv + hv)*ceil(S/64) + chunk.  For stage-level tests of "prepare", which the
  * reference exposes as prepare_workspace (csrc/gdn_chunk/gdn_ops.cu:1026-1030).
  */
@@ -104,7 +104,7 @@ int gdn_chunk_scan_transfers(const float* A, const float* Bm, const float* h0, f
  * passes fixed input/output buffers to its plugins, or a latency-critical loop where cudaMalloc (a
  * device-wide synchronisation) is not acceptable.  The workspace is a fixed 16 MiB array inside the
  * library's device image (held by every GPU that loads the library, for the life of the process), so
- * the problem must satisfy  B * Hv * ceil(S/64) <= 287  (e.g. 4 value heads x 4096 tokens); larger
+ * the problem must satisfy  B * Hv * ceil(S/64) <= 399  (e.g. 4 value heads x 6144 tokens); larger
  * problems return GDN_ERR_SCRATCH and launch nothing.  Arguments and results are those of
  * gdn_chunk_fwd_sm100 with path = GDN_PATH_AUTO.  The call itself allocates nothing.
  * The first call on each device looks up the array's device address (a one-time set-up step); make

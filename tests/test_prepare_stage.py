@@ -63,7 +63,7 @@ def test_prepare_outputs(S, workload):
     tiles = B * Hv * NT
     Wg = raw[off[0]:off[0] + tiles * 16384].view(torch.bfloat16).float().cpu().numpy().reshape(B, Hv, NT, 64, 128)
     Pg = raw[off[1]:off[1] + tiles * 8192].view(torch.bfloat16).float().cpu().numpy().reshape(B, Hv, NT, 64, 64)
-    Ug = raw[off[2]:off[2] + tiles * 32768].view(torch.float32).cpu().numpy().reshape(B, Hv, NT, 64, 128)
+    Ug = raw[off[2]:off[2] + tiles * 16384].view(torch.bfloat16).float().cpu().numpy().reshape(B, Hv, NT, 64, 128)
     vg = raw[off[3]:off[3] + tiles * 1024].view(torch.float32).cpu().numpy().reshape(B, Hv, NT, 256)
     W, U, P, vec = numpy_prepare(*[t.float().numpy().astype(np.float64) for t in (q, k, v, g, beta)])
     # bf16 operands (T rounded to bf16, 8 mantissa bits) bound the accuracy of W and U; P is one rounding

@@ -58,7 +58,7 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row():
 
 def test_noalloc_entry_rejects_problems_beyond_its_fixed_workspace():
     lib = _lib.load()
-    # 32 value heads x 8192 tokens = 4096 tiles > 287: refused on the host, no pointer is touched
+    # 32 value heads x 8192 tokens = 4096 tiles > 399: refused on the host, no pointer is touched
     st = lib.gdn_chunk_fwd_sm100_noalloc(None, None, None, None, None, None, None, None, 1, 8192, 16, 32,
                                          _lib.GATE_F32, None)
     assert st == _lib.GDN_ERR_SCRATCH
