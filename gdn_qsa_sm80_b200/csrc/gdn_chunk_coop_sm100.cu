@@ -32,8 +32,8 @@ struct XSmem {
     // chain ring, one stage:
     static constexpr uint32_t KT = 0, QW = 16384, PB = 49152, UB = 57344, VEC = 61440, kStage = 62464;
     static constexpr uint32_t kStageTx = 16384 + 16384 + 16384 + 8192 + 4096 + 1024;
-    static constexpr uint32_t VN = STAGES * kStage;      // v_new bf16, 64 rows x 64 B
-    static constexpr uint32_t VS = VN + 4096;            // decay-scaled v_new
+    static constexpr uint32_t VN = STAGES * kStage;      // v_new bf16, 2 buffers x 64 rows x 64 B (chunk parity)
+    static constexpr uint32_t VS = VN + 8192;            // decay-scaled v_new
     static constexpr uint32_t SB = VS + 4096;            // bf16 state, 128 rows x 64 B
     // prepare group:
     static constexpr uint32_t PKQ = SB + 8192;           // [K;Q] stack; V replaces Q once Q K^T is done
@@ -161,6 +161,11 @@ __device__ __forceinline__ void coop_prepare_role(uint8_t* sm, uint32_t sm_u32, 
             tma_load_4d(kq + 8192, tm_v, bar_ptma, 0, hv, t * kChunk, b);
             tma_load_4d(kq + 24576, tm_v, bar_ptma, 64, hv, t * kChunk, b);
         }
+        // next tile's gates: a strided global read, issued a whole tile ahead so its latency never shows
+        // (this tile's values were consumed by prep_gates above)
+        if (t + 4 < NT)
+            prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(b) * p.S + (t + 4) * kChunk, hv, p.Hv,
+                                      min(kChunk, p.S - (t + 4) * kChunk), gv, bv, ctx);
         if (t != split) {   // the previous tile's W / U staging tiles (the A and T buffers) have been read by its TMA stores
             mbar_wait_abortable(bar_free, ph_free, p.status, kTimeoutPrepTma, abortp);
             ph_free ^= 1;
@@ -286,9 +291,6 @@ __device__ __forceinline__ void coop_prepare_role(uint8_t* sm, uint32_t sm_u32, 
         ctx.sync();
         // hand the staging tiles to the publisher thread (warp 6): it stores them, frees them and raises the flag
         if (ptid == 0) mbar_arrive(bar_ready);
-        if (tn < NT)
-            prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(b) * p.S + tn * kChunk, hv, p.Hv,
-                                      min(kChunk, p.S - tn * kChunk), gv, bv, ctx);
         GDN_PHASE(7)
         ++prof_n;
     }
@@ -413,7 +415,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                     const uint64_t ad = umma_smem_desc(sb + L::PB + ks * 32, 16, 1024, SWZ_128B);
-                    const uint64_t bd = umma_smem_desc(sm_u32 + L::VN + ks * 16 * L::kRowBytes, 16384, 8 * L::kRowBytes, SWZ_64B);
+                    const uint64_t bd = umma_smem_desc(sm_u32 + L::VN + (t & 1) * 4096 + ks * 16 * L::kRowBytes, 16384, 8 * L::kRowBytes, SWZ_64B);
                     umma_bf16_ss(tmem + kColPV + (t & 1) * NV, ad, bd, idesc_pv, ks > 0);
                 }
                 umma_commit(&bar_pv[t & 1]);
@@ -496,12 +498,9 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const int s = t % STAGES;
             uint8_t* stg = sm + s * L::kStage;
             if (warp >= 2) {
-                ok = mbar_wait_abortable(&bar_d3, t & 1, p.status, kTimeoutD3, abortp) && ok;
-                tc_fence_after_sync();
-                GDN_CPHASE(0)
                 uint32_t w[32];
                 float x[NV], y[NV], u[32];
-                tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV), w);
+                // U does not depend on the state: fetch it while D3 is still in flight
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     const uint4 uv = *reinterpret_cast<const uint4*>(stg + L::UB + swz_chunk_offset<64>(i, ch));
@@ -512,6 +511,10 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         u[8 * ch + 2 * e + 1] = __uint_as_float(uw[e] & 0xffff0000u);
                     }
                 }
+                ok = mbar_wait_abortable(&bar_d3, t & 1, p.status, kTimeoutD3, abortp) && ok;
+                tc_fence_after_sync();
+                GDN_CPHASE(0)
+                tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV), w);
                 tmem_ld_wait();
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
@@ -519,9 +522,9 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     x[c] = vn;
                     y[c] = vn * f_tok;
                 }
-                if (t > 0)
-                    ok = mbar_wait_abortable(&bar_pv[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, kTimeoutPV, abortp) && ok;
-                store_row32_bf16(sm + L::VN, i, x);
+                if (t > 1)   // v_new is double-buffered: only D4 of chunk t-2 must have finished reading this buffer
+                    ok = mbar_wait_abortable(&bar_pv[t & 1], ((t - 2) >> 1) & 1, p.status, kTimeoutPV, abortp) && ok;
+                store_row32_bf16(sm + L::VN + (t & 1) * 4096, i, x);
                 store_row32_bf16(sm + L::VS, i, y);
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
