@@ -363,11 +363,13 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             // ------------------------------- TMA producer of the chain ------------------------------------
             for (int t = 0; t < NT; ++t) {
                 const int s = t % STAGES;
+                // first the flag (an L2 round trip, usually long since raised), then the stage: the flag read
+                // overlaps the time the stage is still in use
+                if (!wait_flag(flags + tile0 + t, p.status, abortp)) break;   // chunk t has been prepared (any CTA of this head)
+                fence_proxy_async_all();     // the workspace was written by another SM; order the TMA reads after the acquire
                 if (t >= STAGES &&
                     !mbar_wait_abortable(&bar_empty[s], ((t / STAGES) - 1) & 1, p.status, kTimeoutEmpty, abortp))
                     break;
-                if (!wait_flag(flags + tile0 + t, p.status, abortp)) break;   // chunk t has been prepared (any CTA of this head)
-                fence_proxy_async_all();     // the workspace was written through the generic proxy, TMA reads it
                 uint8_t* st = sm + s * L::kStage;
                 const int s0 = t * kChunk;
                 const int row0 = static_cast<int>((tile0 + t) * kChunk);
@@ -539,7 +541,6 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         umma_bf16_ss(tmem + kColKV, k0 + ((ks * 2048) >> 4), vs_desc0 + ((ks * 16 * L::kRowBytes) >> 4),
                                      idesc_kv, ks > 0);
                     umma_commit(&bar_kv);
-                    mbar_arrive(&bar_vn);
                 }
                 GDN_CPHASE(2)
             } else if (t > 0) {
@@ -549,7 +550,10 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             ok = mbar_wait_abortable(&bar_kv, t & 1, p.status, kTimeoutKV, abortp) && ok;
             tc_fence_after_sync();
-            if (tid == 0 && ok) mbar_arrive(&bar_empty[s]);
+            if (tid == 0 && ok) {
+                mbar_arrive(&bar_empty[s]);
+                mbar_arrive(&bar_vn);      // D5 is complete: warp 5 may now issue D4 without delaying the critical path
+            }
             GDN_CPHASE(3)
             {
                 uint32_t r[32];
