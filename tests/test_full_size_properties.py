@@ -1,0 +1,80 @@
+"""Checks at the benchmark's full sizes through properties that need no CPU oracle run of that size.
+
+Default workload (B1 S8192 Hq16 Hv32, the configuration the headline metric is quoted on):
+  * two independent device implementations agree: the production path (tcgen05 kernels) against the
+    token-by-token fp32 CUDA-core kernel, which follows the recurrent definition
+    (gdn_qsa_sm80/reference/gdn_chunk_ref.py:133-141) and shares no code with it;
+  * the operator is linear in v: doubling v doubles O and the final state bit for bit (a power-of-two scale
+    commutes with every bf16/fp32 rounding on the way);
+  * splitting the sequence in two and chaining the final state reproduces the unsplit run;
+  * a slice of the result is compared with the CPU oracle run on that slice's prefix only (first 1024 tokens
+    of 4 heads).
+Short-batch workload (B16 S2048): production path against the fp32 kernel on a batch slice.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from gdn_qsa_sm80 import gdn_chunk
+from gdn_qsa_sm80_b200.gdn_chunk_interface import check_device_status
+from gdn_qsa_sm80_b200.synthetic import make_inputs
+
+from helpers import assert_close, oracle_f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def default_problem():
+    q, k, v, g, beta, h0 = make_inputs("default", seed=0)
+    dev = "cuda"
+    d = [t.to(dev) for t in (q, k, v, g, beta, h0)]
+    out, st = gdn_chunk(*d[:5], initial_state=d[5])
+    check_device_status()
+    return (q, k, v, g, beta, h0), d, out, st
+
+
+def test_default_workload_matches_independent_fp32_kernel(default_problem):
+    _, d, out, st = default_problem
+    o2, s2 = gdn_chunk(*d[:5], initial_state=d[5], path="simt")
+    check_device_status()
+    assert_close(out.float().cpu().numpy(), o2.float().cpu().numpy(), "O vs fp32 recurrent kernel")
+    assert_close(st.cpu().numpy(), s2.cpu().numpy(), "final state vs fp32 recurrent kernel")
+
+
+def test_default_workload_is_linear_in_v(default_problem):
+    _, d, out, st = default_problem
+    o2, s2 = gdn_chunk(d[0], d[1], d[2] * 2, d[3], d[4], initial_state=d[5] * 2)
+    check_device_status()
+    assert torch.equal(o2.float(), out.float() * 2)
+    assert torch.equal(s2, st * 2)
+
+
+def test_default_workload_split_and_chain(default_problem):
+    _, d, out, st = default_problem
+    h = d[0].shape[1] // 2
+    oa, sa = gdn_chunk(*[t[:, :h] for t in d[:5]], initial_state=d[5])
+    ob, sb = gdn_chunk(*[t[:, h:] for t in d[:5]], initial_state=sa)
+    check_device_status()
+    assert_close(torch.cat([oa, ob], 1).float().cpu().numpy(), out.float().cpu().numpy(), "chained O", rel=2e-3, mabs=2e-3)
+    assert_close(sb.cpu().numpy(), st.cpu().numpy(), "chained state", rel=1e-4, mabs=1e-4)
+
+
+def test_default_workload_prefix_against_cpu_oracle(default_problem):
+    (q, k, v, g, beta, h0), _, out, _ = default_problem
+    S, heads = 1024, slice(8, 12)          # value heads 8..11 use qk heads 4..5
+    ro, _ = oracle_f32(q[:, :S, 4:6], k[:, :S, 4:6], v[:, :S, heads], g[:, :S, heads], beta[:, :S, heads], h0[:, heads])
+    assert_close(out[:, :S, heads].float().cpu().numpy(), ro, "O prefix vs CPU oracle")
+
+
+def test_short_batch_workload_slice_matches_fp32_kernel():
+    q, k, v, g, beta, _ = make_inputs("short_batch", seed=0)
+    dev = "cuda"
+    d = [t.to(dev) for t in (q, k, v, g, beta)]
+    out, st = gdn_chunk(*d)
+    check_device_status()
+    sl = slice(5, 7)
+    o2, s2 = gdn_chunk(*[t[sl] for t in d], path="simt")
+    assert_close(out[sl].float().cpu().numpy(), o2.float().cpu().numpy(), "O vs fp32 recurrent kernel")
+    assert_close(st[sl].cpu().numpy(), s2.cpu().numpy(), "state vs fp32 recurrent kernel")

@@ -221,3 +221,14 @@ def test_twolevel_scan_matches_serial_path_and_oracle(workload, group_chunks):
     so, ss = run(q, k, v, g, beta, h0, "auto")
     assert_close(out.float().cpu().numpy(), so, "two-level out vs serial")
     assert_close(st.cpu().numpy(), ss, "two-level state vs serial")
+
+
+@pytest.mark.parametrize("Hq,Hv", [(2, 2), (1, 4), (3, 6)])
+def test_head_ratios(Hq, Hv):
+    """Hv / Hq = 1, 4 and 2 with an odd head count (v-head h reads qk-head h // (Hv // Hq))."""
+    q, k, v, g, beta, h0 = bf16_inputs(200, seed=70 + Hv, B=2, Hq=Hq, Hv=Hv, h0=True)
+    ro, rs = oracle_f32(q, k, v, g, beta, h0)
+    for path in ("auto", "twopass_nv64"):
+        out, st = run(q, k, v, g, beta, h0, path)
+        assert_close(out, ro, f"out[{path},Hq={Hq},Hv={Hv}]")
+        assert_close(st, rs, f"state[{path},Hq={Hq},Hv={Hv}]")
