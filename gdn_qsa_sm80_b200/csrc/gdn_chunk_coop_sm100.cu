@@ -307,7 +307,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
                 const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_u,
                 const __grid_constant__ CUtensorMap tm_us, Problem p, Workspace ws,
-                int* flags) {
+                int* flags, int skip_prepare) {
     using L = XSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -356,6 +356,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     volatile int* abortp = &abort_flag;
 
     if (warp >= 8) {
+        if (!skip_prepare)
         coop_prepare_role<GATE_F32>(sm, sm_u32, tmem, tid - 256, &tm_q, &tm_k, &tm_v, p, ws, flags, ps, &bar_ptma, &bar_pmma,
                                     &bar_ready, &bar_free, abortp, split, hv, b, hq, NT, tile0);
     } else if (warp >= 4) {
@@ -384,7 +385,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tma_load_2d(st + L::UB, &tm_u, &bar_full[s], dv0, row0);
                 bulk_load_1d(st + L::VEC, ws.vec + (tile0 + t) * 256, 1024, &bar_full[s]);
             }
-        } else if (warp == 6 && lane == 0) {
+        } else if (warp == 6 && lane == 0 && !skip_prepare) {
             // ------------------------------- publisher of this CTA's prepared tiles ------------------------
             // Stores W and U from the staging tiles, frees the tiles, and raises the tile's flag once the stores
             // are complete; doing this on its own thread keeps the ~3 us write latency off the prepare group.
@@ -608,17 +609,17 @@ bool coop_supported(const Problem& p) {
     return static_cast<long long>(p.B) * p.Hv * (kD / NV) <= sm_count() && p.B <= 65535 && p.Hv <= 65535;
 }
 
-int launch_coop(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream) {
+int launch_coop(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream, bool skip_prepare) {
     if (!coop_supported(p)) return GDN_ERR_BAD_ARGUMENT;
     alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu, tus;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
     if (encode_workspace_maps(p, ws, &tw, &tp, &tus, &tu, NV)) return GDN_ERR_DRIVER;
-    if (cudaMemsetAsync(flags, 0, flag_bytes, stream) != cudaSuccess) return GDN_ERR_CUDA;
+    if (cudaMemsetAsync(flags, skip_prepare ? 1 : 0, flag_bytes, stream) != cudaSuccess) return GDN_ERR_CUDA;
     auto go = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XSmem::kDynamic) != cudaSuccess)
             return GDN_ERR_CUDA;
         const dim3 grid(kD / NV, p.Hv, p.B), block(384);
-        kernel<<<grid, block, XSmem::kDynamic, stream>>>(tq, tk, tv, tw, tp, tu, tus, p, ws, flags);
+        kernel<<<grid, block, XSmem::kDynamic, stream>>>(tq, tk, tv, tw, tp, tu, tus, p, ws, flags, skip_prepare ? 1 : 0);
         count_launch();
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };
