@@ -32,9 +32,10 @@ PATH_PREPARE_ONLY = 6
 PATH_CHAIN_ONLY = 7
 PATH_COOP = 8
 PATH_COOP_CHAIN_ONLY = 9
+PATH_COOP_DEDICATED = 10
 PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "fused_nv64": PATH_FUSED_NV64, "fused_nv32": PATH_FUSED_NV32,
          "twopass_nv64": PATH_TWOPASS_NV64, "twopass_nv32": PATH_TWOPASS_NV32,
-         "prepare_only": PATH_PREPARE_ONLY, "chain_only": PATH_CHAIN_ONLY, "coop": PATH_COOP, "coop_chain_only": PATH_COOP_CHAIN_ONLY}
+         "prepare_only": PATH_PREPARE_ONLY, "chain_only": PATH_CHAIN_ONLY, "coop": PATH_COOP, "coop_chain_only": PATH_COOP_CHAIN_ONLY, "coop_dedicated": PATH_COOP_DEDICATED}
 
 # Every symbol the public header declares (checked by the CPU tests).
 EXPORTS = (

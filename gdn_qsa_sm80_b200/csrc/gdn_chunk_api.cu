@@ -121,7 +121,7 @@ static size_t tiles_of(int B, int S, int Hv) {
 static bool path_uses_workspace(int path) {
     return path == GDN_PATH_AUTO || path == GDN_PATH_TWOPASS_NV64 || path == GDN_PATH_TWOPASS_NV32 ||
            path == GDN_PATH_PREPARE_ONLY || path == GDN_PATH_CHAIN_ONLY || path == GDN_PATH_COOP ||
-           path == GDN_PATH_COOP_CHAIN_ONLY;
+           path == GDN_PATH_COOP_CHAIN_ONLY || path == GDN_PATH_COOP_DEDICATED;
 }
 
 size_t gdn_chunk_scratch_bytes(int B, int S, int Hq, int Hv, int path) {
@@ -145,7 +145,7 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
-    if (path < GDN_PATH_AUTO || path > GDN_PATH_COOP_CHAIN_ONLY) return GDN_ERR_BAD_ARGUMENT;
+    if (path < GDN_PATH_AUTO || path > GDN_PATH_COOP_DEDICATED) return GDN_ERR_BAD_ARGUMENT;
     if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u) ||
         scratch_bytes < gdn_chunk_scratch_bytes(B, S, Hq, Hv, path))
         return GDN_ERR_SCRATCH;
@@ -192,6 +192,8 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
     ws.P = reinterpret_cast<__nv_bfloat16*>(base + l.P);
     ws.U = reinterpret_cast<__nv_bfloat16*>(base + l.U);
     ws.vec = reinterpret_cast<float*>(base + l.vec);
+    if (path == GDN_PATH_COOP_DEDICATED)
+        return launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, false, true);
     if (path == GDN_PATH_COOP_CHAIN_ONLY)
         return launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, true);
     // few independent sequences: one launch in which a head's four column CTAs share the prepare work

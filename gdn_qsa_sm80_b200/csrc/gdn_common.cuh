@@ -72,9 +72,11 @@ int launch_chain(const Problem& p, const Workspace& ws, int nv, cudaStream_t str
 // Single-launch variant (prepare shared among the four column CTAs of a head, chain in the same kernel);
 // only when all CTAs fit on the GPU at once.
 bool coop_supported(const Problem& p);
+bool coop_dedicated_supported(const Problem& p);
 // skip_prepare (measurement aid): run only the chain roles on a workspace an earlier call left behind.
+// dedicated: 64-column chain CTAs on their own SMs, prepare groups on the remaining SMs.
 int launch_coop(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream,
-                bool skip_prepare = false);
+                bool skip_prepare = false, bool dedicated = false);
 
 // Host helper: encode a tiled TMA descriptor for a row-major tensor of `rank` dims
 // (dims/strides innermost first; strides in bytes for dims 1..rank-1).  swizzle_bytes: 128 or 64.

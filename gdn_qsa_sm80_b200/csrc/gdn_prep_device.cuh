@@ -16,7 +16,7 @@ constexpr int kSolveStride = 68;   // fp32 row stride of the 64x64 solve matrice
 constexpr int kY1Stride = 20;      // row stride of the 16-column temporaries of merge level 1
 constexpr int kY2Stride = 36;      // row stride of the 32-column temporary of merge level 2
 
-struct PrepScratch {
+struct alignas(16) PrepScratch {
     float gam[kChunk];        // gamma_j * log2(e): inclusive cumsum of the log gate inside the chunk
     float bet[kChunk];        // beta_j (0 for padding tokens)
     float eg[kChunk];         // beta_j * exp(gamma_j)

@@ -42,6 +42,8 @@ extern "C" {
                                     call with the same arguments and scratch left behind              */
 #define GDN_PATH_COOP 8          /* one launch: the four 32-column CTAs of a head share the prepare work
                                     through the workspace while their chains run; needs 4*B*Hv <= #SMs    */
+#define GDN_PATH_COOP_DEDICATED 10 /* one launch: 64-column chain CTAs (2 per head) on SMs of their own, prepare
+                                    groups on all remaining SMs; needs 8*B*Hv <= 3*#SMs                   */
 #define GDN_PATH_COOP_CHAIN_ONLY 9 /* measurement aid: COOP with its prepare roles switched off, on the
                                     workspace an earlier call with the same arguments and scratch left  */
 
