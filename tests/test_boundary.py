@@ -50,7 +50,7 @@ def test_argument_validation_before_any_cuda_call():
     args = [None] * 8
     assert L.gdn_chunk_fwd_sm100(*args, None, 0, 1, 64, 3, 4, 0, 0, None) == _lib.GDN_ERR_BAD_ARGUMENT
     assert L.gdn_chunk_fwd_sm100(*args, None, 0, 1, 64, 2, 4, 7, 0, None) == _lib.GDN_ERR_BAD_ARGUMENT
-    assert L.gdn_chunk_fwd_sm100(*args, None, 0, 1, 64, 2, 4, 0, 9, None) == _lib.GDN_ERR_BAD_ARGUMENT
+    assert L.gdn_chunk_fwd_sm100(*args, None, 0, 1, 64, 2, 4, 0, 99, None) == _lib.GDN_ERR_BAD_ARGUMENT
     assert L.gdn_chunk_fwd_sm100(*args, None, 0, 1, 64, 2, 4, 0, 0, None) == _lib.GDN_ERR_SCRATCH
 
 
