@@ -33,6 +33,8 @@ PATH_CHAIN_ONLY = 7
 PATH_COOP = 8
 PATH_COOP_CHAIN_ONLY = 9
 PATH_COOP_DEDICATED = 10
+FLAG_QK_L2NORM = 1
+
 PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "fused_nv64": PATH_FUSED_NV64, "fused_nv32": PATH_FUSED_NV32,
          "twopass_nv64": PATH_TWOPASS_NV64, "twopass_nv32": PATH_TWOPASS_NV32,
          "prepare_only": PATH_PREPARE_ONLY, "chain_only": PATH_CHAIN_ONLY, "coop": PATH_COOP, "coop_chain_only": PATH_COOP_CHAIN_ONLY, "coop_dedicated": PATH_COOP_DEDICATED}
@@ -42,6 +44,7 @@ EXPORTS = (
     "gdn_chunk_scratch_bytes",
     "gdn_chunk_workspace_offsets",
     "gdn_chunk_fwd_sm100",
+    "gdn_chunk_fwd_sm100_ex",
     "gdn_chunk_fwd_sm100_noalloc",
     "gdn_chunk_scan_transfers",
     "gdn_chunk_read_status",
@@ -76,6 +79,8 @@ def load() -> ctypes.CDLL:
     lib.gdn_chunk_workspace_offsets.restype = ci
     lib.gdn_chunk_fwd_sm100.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, vp]
     lib.gdn_chunk_fwd_sm100.restype = ci
+    lib.gdn_chunk_fwd_sm100_ex.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, ctypes.c_uint, vp]
+    lib.gdn_chunk_fwd_sm100_ex.restype = ci
     lib.gdn_chunk_fwd_sm100_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]
     lib.gdn_chunk_fwd_sm100_noalloc.restype = ci
     lib.gdn_chunk_scan_transfers.argtypes = [vp, vp, vp, vp, vp, ci, ci, vp]

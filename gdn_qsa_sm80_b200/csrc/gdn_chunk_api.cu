@@ -142,7 +142,18 @@ int gdn_chunk_workspace_offsets(int B, int S, int Hq, int Hv, size_t* offsets) {
 int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
                         const float* h0, void* out, float* hT, void* scratch, size_t scratch_bytes,
                         int B, int S, int Hq, int Hv, int gate_dtype, int path, void* stream_) {
+    return gdn_chunk_fwd_sm100_ex(q, k, v, g, beta, h0, out, hT, scratch, scratch_bytes, B, S, Hq, Hv, gate_dtype,
+                                  path, 0u, stream_);
+}
+
+int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                           const float* h0, void* out, float* hT, void* scratch, size_t scratch_bytes,
+                           int B, int S, int Hq, int Hv, int gate_dtype, int path, unsigned flags, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (flags & ~static_cast<unsigned>(GDN_FLAG_QK_L2NORM)) return GDN_ERR_BAD_ARGUMENT;
+    // the first-generation fused kernel has no normalisation; every other path folds it into its factors
+    if ((flags & GDN_FLAG_QK_L2NORM) && (path == GDN_PATH_FUSED_NV64 || path == GDN_PATH_FUSED_NV32))
+        return GDN_ERR_BAD_ARGUMENT;
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
     if (path < GDN_PATH_AUTO || path > GDN_PATH_COOP_DEDICATED) return GDN_ERR_BAD_ARGUMENT;
@@ -176,6 +187,7 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
     p.prof = g_phase_profile;
     p.B = B; p.S = S; p.Hq = Hq; p.Hv = Hv;
     p.gate_f32 = gate_dtype == GDN_GATE_F32;
+    p.l2norm = (flags & GDN_FLAG_QK_L2NORM) ? 1 : 0;
 
     if (path == GDN_PATH_SIMT) return launch_simt(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     if (path == GDN_PATH_FUSED_NV64) return launch_fused(p, 64, stream);

@@ -142,7 +142,7 @@ __device__ __forceinline__ void prepare_role(const PrepRes& r, int ptid, const C
     PrepScratch& ps = *r.ps;
     const int pwarp = ptid >> 5, i = ptid & 63;
     const uint32_t lane_base = static_cast<uint32_t>(pwarp) * 32u;
-    const float scale = rsqrtf(static_cast<float>(kD));
+    const float scale0 = rsqrtf(static_cast<float>(kD));
     const int NT = sched.NT, rep = p.Hv / p.Hq;
     float* As = reinterpret_cast<float*>(r.sm + PAS);
     float* Tm = reinterpret_cast<float*>(r.sm + PTM);
@@ -185,7 +185,7 @@ __device__ __forceinline__ void prepare_role(const PrepRes& r, int ptid, const C
         const size_t tile = (static_cast<size_t>(b) * p.Hv + hv) * NT + t;
         int bn, hvn, tn;
         const bool have_next = sched.get(n + 1, bn, hvn, tn);
-        prep_gates(ps, gv, bv, scale, ws.vec + tile * 256, ctx);
+        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, ctx);
         ctx.sync();
         GDN_PHASE(0)
         mbar_wait_abortable(r.tma, ph_tma, p.status, kTimeoutPrepTma, abortp);
@@ -201,6 +201,7 @@ __device__ __forceinline__ void prepare_role(const PrepRes& r, int ptid, const C
             }
             umma_commit(r.mma);
         }
+        if (p.l2norm) prep_l2norm_fold(ps, kq, ws.vec + tile * 256, ctx);   // while the UMMAs run
         mbar_wait_abortable(r.mma, ph_mma, p.status, kTimeoutPrepMma, abortp);
         ph_mma ^= 1;
         tc_fence_after_sync();
@@ -220,11 +221,13 @@ __device__ __forceinline__ void prepare_role(const PrepRes& r, int ptid, const C
         prep_zero_upper_blocks(Tm, ctx);
         {
             float ri, diag[16];
-            prep_row_setup(ps, i, ri, diag);
+            if (p.l2norm) prep_row_setup_l2(ps, i, ri, diag);
+            else prep_row_setup(ps, i, ri, diag);
+            const float scale = p.l2norm ? scale0 * ps.rn[kChunk + i] : scale0;   // row factor of P
             uint32_t rr[32];
             float f[32];
             if (pwarp < 2) {
-                const float bi = ps.bet[i];
+                const float bi = p.l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     tmem_ld_x32(tmem_addr(tm_prep, lane_base, half * 32), rr);

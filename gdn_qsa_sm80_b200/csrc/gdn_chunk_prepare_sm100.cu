@@ -55,7 +55,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     __shared__ __align__(16) PrepScratch ps;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const float scale = rsqrtf(static_cast<float>(kD));
+    const float scale0 = rsqrtf(static_cast<float>(kD));
     const int i = tid & 63;
 
     // Persistent CTA: tiles L = blockIdx.x, blockIdx.x + gridDim.x, ...  L -> (b, chunk t, head hv) with the
@@ -123,7 +123,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const size_t tile = cur.ws_tile;
         // the previous tile's W/U stores must have finished reading their staging buffers
         if (tid == 0) tma_store_wait_read();
-        prep_gates(ps, gv, bv, scale, ws.vec + tile * 256);
+        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256);
         prep_zero_upper_blocks(Tm);
         __syncthreads();
         GDN_PHASE(0)
@@ -144,6 +144,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             umma_commit(&bar_mma);
         }
+        if (p.l2norm) prep_l2norm_fold(ps, sm + PSmem::KQ, ws.vec + tile * 256);   // while the UMMAs run
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
         ok = __syncthreads_and(ok);
@@ -153,11 +154,13 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tc_fence_after_sync();
         {
             float ri, diag[16];
-            prep_row_setup(ps, i, ri, diag);
+            if (p.l2norm) prep_row_setup_l2(ps, i, ri, diag);
+            else prep_row_setup(ps, i, ri, diag);
+            const float scale = p.l2norm ? scale0 * ps.rn[kChunk + i] : scale0;   // row factor of P
             uint32_t r[32];
             float f[32];
             if (warp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
-                const float bi = ps.bet[i];
+                const float bi = p.l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);

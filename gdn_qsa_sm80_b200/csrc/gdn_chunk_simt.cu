@@ -49,19 +49,30 @@ __global__ void __launch_bounds__(128) gdn_recurrent_simt_kernel(Problem p) {
         const float vi = v_n, dec = __expf(g_n), bt = b_n;
         if (i + 1 < p.S) fetch(i + 1);
         __syncthreads();
-        float kv = 0.f;
+        float kv = 0.f, rk = 1.f, rq = 1.f;
+        if (p.l2norm) {   // every thread sums the squares itself: the vectors are in shared memory anyway
+            float kk = 0.f, qq = 0.f;
+#pragma unroll
+            for (int r = 0; r < kD; ++r) {
+                kk = fmaf(ks[buf][r], ks[buf][r], kk);
+                qq = fmaf(qs[buf][r], qs[buf][r], qq);
+            }
+            rk = rsqrtf(kk + 1e-6f);
+            rq = rsqrtf(qq / (scale * scale) + 1e-6f);   // qs holds q * scale
+        }
 #pragma unroll
         for (int r = 0; r < kD; ++r) {
             st[r] *= dec;
             kv = fmaf(st[r], ks[buf][r], kv);
         }
-        const float dl = (vi - kv) * bt;
+        const float dl = (vi - kv * rk) * bt * rk;
         float o = 0.f;
 #pragma unroll
         for (int r = 0; r < kD; ++r) {
             st[r] = fmaf(ks[buf][r], dl, st[r]);
             o = fmaf(st[r], qs[buf][r], o);
         }
+        o *= rq;
         p.out[((static_cast<size_t>(b) * p.S + i) * p.Hv + h) * kD + c] = __float2bfloat16(o);
     }
     if (p.hT) {

@@ -26,6 +26,7 @@ struct Problem {
     long long* prof;       // optional: 16 per-phase cycle counters written by CTA (0,0,0); null = off
     int B, S, Hq, Hv;
     int gate_f32;          // 0: g/beta are bf16, 1: fp32
+    int l2norm;            // 1: q and k are L2-normalised per head vector inside the kernels
 };
 
 // Workspace of the two-kernel path (device pointers into the caller's scratch buffer).

@@ -21,6 +21,7 @@ struct alignas(16) PrepScratch {
     float bet[kChunk];        // beta_j (0 for padding tokens)
     float eg[kChunk];         // beta_j * exp(gamma_j)
     float ctab[3][kChunk];    // ctab[I-1][j] = exp(gamma_{16 I} - gamma_j) for j < 16 I  (always <= 1)
+    float rn[2 * kChunk];     // optional in-kernel L2 normalisation: 1/|k_j| (0..63) and 1/|q_i| (64..127), else unused
     float wsum[2];
 };
 
@@ -122,6 +123,51 @@ __device__ __forceinline__ void prep_row_factors(const PrepScratch& ps, int i, i
     }
 }
 
+// In-kernel L2 normalisation of q and k (the reference's torch definition has it as use_qk_l2norm_in_kernel,
+// gdn_qsa_sm80/reference/gdn_chunk_ref.py:15-17, :43-45: x * rsqrt(sum x^2 + 1e-6)).  Nothing is rewritten in the
+// tiles: the inverse norms are folded into factors that exist anyway.  With rk_j = 1/|k_j|, rq_i = 1/|q_i|:
+//   K K^T, Q K^T columns  -> the decay tables (ctab here, the diagonal factors in prep_row_setup_l2)
+//   rows of A / P         -> beta_i rk_i and scale rq_i (callers)
+//   W = T (beta e^gamma K)-> eg_j rk_j
+//   K^T v~ and (Q S) later-> the per-token factors in vec_out: exp(gamma_C-gamma_i) rk_i and scale exp(gamma_i) rq_i
+// `kq` is the [K;Q] stack (two k-halves of 128 rows x 128 bytes, 128-byte swizzle; the swizzle only permutes the
+// 16-byte chunks inside a row, so a row's sum of squares needs no un-swizzling).  Thread r handles row r.
+// Contains two group barriers; call after the tiles have landed and before the tables are used.
+__device__ __forceinline__ void prep_l2norm_fold(PrepScratch& ps, const uint8_t* kq, float* vec_out,
+                                                 PrepCtx ctx = PrepCtx::whole_cta()) {
+    const int tid = ctx.tid;
+    float ss = 0.f;
+#pragma unroll
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+            // rotate the chunk order by the row number: rows are 128 B apart, so this spreads a warp over the banks
+            const uint4 v = *reinterpret_cast<const uint4*>(kq + half * 16384 + tid * 128 + ((ch + tid) & 7) * 16);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
+                ss = fmaf(lo, lo, ss);
+                ss = fmaf(hi, hi, ss);
+            }
+        }
+    ps.rn[tid] = rsqrtf(ss + 1e-6f);
+    ctx.sync();
+    if (tid < kChunk) {
+        ps.eg[tid] *= ps.rn[tid];
+        if (vec_out) {
+            vec_out[tid] *= ps.rn[tid];
+            vec_out[kChunk + tid] *= ps.rn[kChunk + tid];
+        }
+    }
+    if (tid < 96) {
+        const int I = tid < 16 ? 1 : (tid < 48 ? 2 : 3);
+        const int j = tid - (I == 1 ? 0 : (I == 2 ? 16 : 48));
+        ps.ctab[I - 1][j] *= ps.rn[j];
+    }
+    ctx.sync();
+}
+
 // Per-thread setup for prep_row_factors: ri and the 16 diagonal-block factors of row i.
 __device__ __forceinline__ void prep_row_setup(const PrepScratch& ps, int i, float& ri, float (&diag)[16]) {
     const int I = i >> 4, ii = i & 15;
@@ -129,6 +175,14 @@ __device__ __forceinline__ void prep_row_setup(const PrepScratch& ps, int i, flo
     ri = exp2f(gi - ps.gam[16 * I]);
 #pragma unroll
     for (int jj = 0; jj < 16; ++jj) diag[jj] = (jj <= ii) ? exp2f(gi - ps.gam[16 * I + jj]) : 0.f;
+}
+
+// Same with the column norms 1/|k_j| folded into the diagonal-block factors (L2 normalisation on).
+__device__ __forceinline__ void prep_row_setup_l2(const PrepScratch& ps, int i, float& ri, float (&diag)[16]) {
+    prep_row_setup(ps, i, ri, diag);
+    const int I = i >> 4;
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) diag[jj] *= ps.rn[16 * I + jj];
 }
 
 __device__ __forceinline__ uint32_t f32_to_tf32(float x) {

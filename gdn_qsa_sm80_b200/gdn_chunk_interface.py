@@ -55,7 +55,7 @@ def _scratch_for(device, nbytes):
     return buf
 
 
-def _forward(q, k, v, g, beta, output_final_state, initial_state, path):
+def _forward(q, k, v, g, beta, output_final_state, initial_state, path, l2norm=False):
     q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
     B, S, Hk, Hv = _check_inputs(q, k, v, g, beta)
     if not q.is_cuda:
@@ -83,12 +83,12 @@ def _forward(q, k, v, g, beta, output_final_state, initial_state, path):
         nbytes = int(lib.gdn_chunk_scratch_bytes(B, S, Hk, Hv, code))
         scratch = _scratch_for(dev, nbytes)
         stream = torch.cuda.current_stream(dev).cuda_stream
-        st = lib.gdn_chunk_fwd_sm100(
+        st = lib.gdn_chunk_fwd_sm100_ex(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
             h0.data_ptr() if h0 is not None else None, out.data_ptr(),
             hT.data_ptr() if hT is not None else None, scratch.data_ptr(), scratch.numel(),
-            B, S, Hk, Hv, gate, code, stream)
-        _lib.check(st, "gdn_chunk_fwd_sm100")
+            B, S, Hk, Hv, gate, code, _lib.FLAG_QK_L2NORM if l2norm else 0, stream)
+        _lib.check(st, "gdn_chunk_fwd_sm100_ex")
         if os.environ.get("GDN_CHUNK_CHECK_STATUS", "0") == "1":
             check_device_status(dev)
     return out, hT
@@ -109,7 +109,8 @@ def check_device_status(device=None):
         raise _lib.GdnLibraryError(f"device status 0x{word.value:x}: {_lib.error_string(st)}")
 
 
-def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, path="auto"):
+def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, path="auto",
+              use_qk_l2norm_in_kernel=False):
     """GDN forward (chunked gated delta rule).
 
     Args:
@@ -118,12 +119,14 @@ def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, pat
         g, beta: [B, S, Hv] bf16 or fp32 - log-decay (<= 0) and update gate.
         output_final_state: whether to return the final state.
         initial_state: optional [B, Hv, D, D] state to start from (zeros when None).
-        path: "auto", or one of "simt", "fused_nv64", "fused_nv32" to force a kernel.
+        path: "auto", or a key of `_lib.PATHS` to force a kernel.
+        use_qk_l2norm_in_kernel: L2-normalise every q and k head vector inside the kernels, the switch of the
+            reference's torch definition (reference/gdn_chunk_ref.py:29, :43-45); not on the "fused_*" paths.
 
     Returns:
         out [B, S, Hv, D] bf16, and final_state [B, Hv, D, D] fp32 (None when not requested).
     """
-    return _forward(q, k, v, g, beta, output_final_state, initial_state, path)
+    return _forward(q, k, v, g, beta, output_final_state, initial_state, path, bool(use_qk_l2norm_in_kernel))
 
 
 def scan_transfers(A, Bm, h0=None):

@@ -47,6 +47,9 @@ extern "C" {
 #define GDN_PATH_COOP_CHAIN_ONLY 9 /* measurement aid: COOP with its prepare roles switched off, on the
                                     workspace an earlier call with the same arguments and scratch left  */
 
+/* option bits of gdn_chunk_fwd_sm100_ex */
+#define GDN_FLAG_QK_L2NORM 1u    /* normalise every q and k head vector: x * rsqrt(sum x^2 + 1e-6)    */
+
 #define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
 #define GDN_CHUNK 64             /* tokens per chunk                                                */
 
@@ -88,6 +91,18 @@ int gdn_chunk_workspace_offsets(int B, int S, int Hq, int Hv, size_t* offsets);
 int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
                         const float* h0, void* out, float* hT, void* scratch, size_t scratch_bytes,
                         int B, int S, int Hq, int Hv, int gate_dtype, int path, void* stream);
+
+/*
+ * gdn_chunk_fwd_sm100 with option bits.  GDN_FLAG_QK_L2NORM: q and k are L2-normalised per token and
+ * head inside the kernels (fp32, x * rsqrt(sum x^2 + 1e-6)), as use_qk_l2norm_in_kernel does in the
+ * reference's torch definition (gdn_qsa_sm80/reference/gdn_chunk_ref.py:15-17, :43-45, :116-118); the
+ * reference's CUDA kernels expect normalised inputs and have no such switch, so callers there normalise
+ * in a separate pass over q and k.  Not available on the GDN_PATH_FUSED_* paths (GDN_ERR_BAD_ARGUMENT);
+ * unknown bits are rejected.  flags = 0 is gdn_chunk_fwd_sm100.
+ */
+int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                           const float* h0, void* out, float* hT, void* scratch, size_t scratch_bytes,
+                           int B, int S, int Hq, int Hv, int gate_dtype, int path, unsigned flags, void* stream);
 
 /*
  * Second level of the two-level chunk scan.  A [n_seq][G][128][128] and Bm (same shape), fp32: group g

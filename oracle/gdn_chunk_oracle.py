@@ -34,6 +34,7 @@ __all__ = [
     "expand_qk_heads",
     "rel_l2",
     "max_abs",
+    "l2norm",
 ]
 
 
@@ -43,6 +44,11 @@ def expand_qk_heads(x: np.ndarray, hv: int) -> np.ndarray:
     if hv % hk:
         raise ValueError(f"Hv={hv} is not a multiple of Hk={hk}")
     return np.repeat(x, hv // hk, axis=2)
+
+
+def l2norm(x: np.ndarray, eps: float = 1e-6) -> np.ndarray:
+    """x * rsqrt(sum x^2 + eps) over the last axis (gdn_chunk_ref.py:15-17)."""
+    return x / np.sqrt((x * x).sum(axis=-1, keepdims=True) + x.dtype.type(eps))
 
 
 def _solve_unit_lower(a: np.ndarray, rhs: np.ndarray) -> np.ndarray:
@@ -60,7 +66,7 @@ def _solve_unit_lower(a: np.ndarray, rhs: np.ndarray) -> np.ndarray:
 
 
 def chunk_gated_delta_rule(q, k, v, g, beta, chunk_size=64, initial_state=None,
-                           output_final_state=True, dtype=np.float64):
+                           output_final_state=True, dtype=np.float64, use_qk_l2norm_in_kernel=False):
     """Chunked gated delta rule; returns (out [B,S,Hv,Dv], final_state or None).
 
     Step numbers in the comments are line numbers of gdn_chunk_ref.py.
@@ -68,6 +74,8 @@ def chunk_gated_delta_rule(q, k, v, g, beta, chunk_size=64, initial_state=None,
     q, k, v, g, beta = (np.asarray(x, dtype=dtype) for x in (q, k, v, g, beta))
     b, s, hv, dv = v.shape
     dk = k.shape[-1]
+    if use_qk_l2norm_in_kernel:   # :43-45
+        q, k = l2norm(q), l2norm(k)
     q = expand_qk_heads(q, hv)
     k = expand_qk_heads(k, hv)
     # :39-42 head-major; :46-47 query scaling
@@ -119,11 +127,13 @@ def chunk_gated_delta_rule(q, k, v, g, beta, chunk_size=64, initial_state=None,
 
 
 def recurrent_gated_delta_rule(q, k, v, g, beta, initial_state=None,
-                               output_final_state=True, dtype=np.float64):
+                               output_final_state=True, dtype=np.float64, use_qk_l2norm_in_kernel=False):
     """Token-by-token gated delta rule (gdn_chunk_ref.py:103-147)."""
     q, k, v, g, beta = (np.asarray(x, dtype=dtype) for x in (q, k, v, g, beta))
     b, s, hv, dv = v.shape
     dk = k.shape[-1]
+    if use_qk_l2norm_in_kernel:   # :116-118
+        q, k = l2norm(q), l2norm(k)
     q = expand_qk_heads(q, hv) / dtype(dk) ** dtype(0.5)   # :123
     k = expand_qk_heads(k, hv)
     if initial_state is None:

@@ -29,9 +29,12 @@ def checksum(*tensors) -> str:
     return h.hexdigest()
 
 
-def oracle_f32(q, k, v, g, beta, h0=None, form="chunk"):
-    """fp32 C oracle on torch CPU tensors (values upcast as they are); returns numpy arrays."""
+def oracle_f32(q, k, v, g, beta, h0=None, form="chunk", l2norm=False):
+    """fp32 C oracle on torch CPU tensors (values upcast as they are); returns numpy arrays.
+    l2norm: normalise q and k first, in fp32, as the reference's use_qk_l2norm_in_kernel does."""
     args = [x.detach().float().cpu().numpy() for x in (q, k, v, g, beta)]
+    if l2norm:
+        args[0], args[1] = np_oracle.l2norm(args[0]), np_oracle.l2norm(args[1])
     h = None if h0 is None else h0.detach().float().cpu().numpy()
     fn = c_oracle.chunk_f32 if form == "chunk" else c_oracle.recurrent_f32
     return fn(*args, initial_state=h)

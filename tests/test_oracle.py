@@ -50,6 +50,25 @@ def test_c_oracle_matches_reference(name, form):
     assert O.rel_l2(st, z[f"state_{form}"]) < TOL
 
 
+@pytest.mark.parametrize("form", ["chunk", "recurrent"])
+def test_l2norm_switch_matches_reference(form):
+    # golden made by the reference with use_qk_l2norm_in_kernel=True on un-normalised q/k
+    z, x, _ = _case("l2norm.npz")
+    fn = O.chunk_gated_delta_rule if form == "chunk" else O.recurrent_gated_delta_rule
+    out, st = fn(*x, use_qk_l2norm_in_kernel=True)
+    assert O.rel_l2(out, z[f"out_{form}"]) < TOL
+    assert O.rel_l2(st, z[f"state_{form}"]) < TOL
+    # the fp32 C oracle on inputs normalised beforehand in fp32 (how the GPU tests use it)
+    q, k = (O.l2norm(a.astype(np.float32)) for a in x[:2])
+    cfn = c_oracle.chunk_f32 if form == "chunk" else c_oracle.recurrent_f32
+    out, st = cfn(q, k, *x[2:])
+    assert O.rel_l2(out, z[f"out_{form}"]) < TOL
+    assert O.rel_l2(st, z[f"state_{form}"]) < TOL
+    # and the switch matters on these inputs
+    out_off, _ = fn(*x)
+    assert O.rel_l2(out_off, z[f"out_{form}"]) > 0.1
+
+
 def test_cpu_small_workload_matches_reference():
     """The CPU benchmark workload (B1 S512 Hq4 Hv8 fp32 seed 0) regenerated from its seed."""
     z = golden("cpu_small.npz")
