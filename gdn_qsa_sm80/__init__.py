@@ -6,8 +6,9 @@ from gdn_qsa_sm80_b200 import (  # noqa: F401
     GDN_CHUNK,
     GDN_D,
     gdn_chunk,
+    gdn_chunk_host,
     gdn_chunk_reference,
     gdn_chunk_twolevel,
 )
 
-__all__ = ["gdn_chunk", "gdn_chunk_twolevel", "gdn_chunk_reference"]
+__all__ = ["gdn_chunk", "gdn_chunk_host", "gdn_chunk_twolevel", "gdn_chunk_reference"]

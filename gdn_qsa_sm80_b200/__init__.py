@@ -4,9 +4,10 @@ from .gdn_chunk_interface import (
     GDN_CHUNK,
     GDN_D,
     gdn_chunk,
+    gdn_chunk_host,
     gdn_chunk_reference,
     gdn_chunk_twolevel,
 )
 
 __version__ = "0.1.0"
-__all__ = ["gdn_chunk", "gdn_chunk_twolevel", "gdn_chunk_reference", "GDN_D", "GDN_CHUNK"]
+__all__ = ["gdn_chunk", "gdn_chunk_host", "gdn_chunk_twolevel", "gdn_chunk_reference", "GDN_D", "GDN_CHUNK"]

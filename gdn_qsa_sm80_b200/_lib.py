@@ -45,6 +45,8 @@ EXPORTS = (
     "gdn_chunk_workspace_offsets",
     "gdn_chunk_fwd_sm100",
     "gdn_chunk_fwd_sm100_ex",
+    "gdn_chunk_host_arena_bytes",
+    "gdn_chunk_fwd_host_sm100",
     "gdn_chunk_fwd_sm100_noalloc",
     "gdn_chunk_scan_transfers",
     "gdn_chunk_read_status",
@@ -81,6 +83,10 @@ def load() -> ctypes.CDLL:
     lib.gdn_chunk_fwd_sm100.restype = ci
     lib.gdn_chunk_fwd_sm100_ex.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, ctypes.c_uint, vp]
     lib.gdn_chunk_fwd_sm100_ex.restype = ci
+    lib.gdn_chunk_host_arena_bytes.argtypes = [ci] * 6
+    lib.gdn_chunk_host_arena_bytes.restype = sz
+    lib.gdn_chunk_fwd_host_sm100.argtypes = [vp] * 9 + [sz] + [ci] * 6 + [ctypes.c_uint, vp]
+    lib.gdn_chunk_fwd_host_sm100.restype = ci
     lib.gdn_chunk_fwd_sm100_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]
     lib.gdn_chunk_fwd_sm100_noalloc.restype = ci
     lib.gdn_chunk_scan_transfers.argtypes = [vp, vp, vp, vp, vp, ci, ci, vp]

@@ -149,7 +149,16 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
 int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const void* g, const void* beta,
                            const float* h0, void* out, float* hT, void* scratch, size_t scratch_bytes,
                            int B, int S, int Hq, int Hv, int gate_dtype, int path, unsigned flags, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    return forward_device(q, k, v, g, beta, h0, out, hT, scratch, scratch_bytes, B, S, Hq, Hv, gate_dtype, path,
+                          flags, static_cast<cudaStream_t>(stream_), true);
+}
+
+}  // extern "C"
+
+namespace gdn {
+int forward_device(const void* q, const void* k, const void* v, const void* g, const void* beta, const float* h0,
+                   void* out, float* hT, void* scratch, size_t scratch_bytes, int B, int S, int Hq, int Hv,
+                   int gate_dtype, int path, unsigned flags, cudaStream_t stream, bool clear_status) {
     if (flags & ~static_cast<unsigned>(GDN_FLAG_QK_L2NORM)) return GDN_ERR_BAD_ARGUMENT;
     // the first-generation fused kernel has no normalisation; every other path folds it into its factors
     if ((flags & GDN_FLAG_QK_L2NORM) && (path == GDN_PATH_FUSED_NV64 || path == GDN_PATH_FUSED_NV32))
@@ -160,7 +169,7 @@ int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const vo
     if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u) ||
         scratch_bytes < gdn_chunk_scratch_bytes(B, S, Hq, Hv, path))
         return GDN_ERR_SCRATCH;
-    if (cudaMemsetAsync(scratch, 0, 256, stream) != cudaSuccess) return GDN_ERR_CUDA;
+    if (clear_status && cudaMemsetAsync(scratch, 0, 256, stream) != cudaSuccess) return GDN_ERR_CUDA;
     if (S == 0) {   // nothing to scan: the final state is the initial state
         if (hT) {
             const size_t bytes = static_cast<size_t>(B) * Hv * kD * kD * sizeof(float);
@@ -216,6 +225,9 @@ int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const vo
     if (st != GDN_OK || path == GDN_PATH_PREPARE_ONLY) return st;
     return launch_chain(p, ws, nv, stream);
 }
+}  // namespace gdn
+
+extern "C" {
 
 int gdn_chunk_read_status(const void* scratch, void* stream_, int* device_status) {
     if (!scratch || !device_status) return GDN_ERR_BAD_ARGUMENT;

@@ -94,6 +94,11 @@ inline int encode_tma_bf16(void* tmap_out, const void* base, int rank, const uns
 int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu_store, void* tu_load, int nv);
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// The forward pass on device buffers (what gdn_chunk_fwd_sm100_ex does).  clear_status = false leaves the status
+// word at the start of `scratch` as it is, so that several launches can share one sticky word.
+int forward_device(const void* q, const void* k, const void* v, const void* g, const void* beta, const float* h0,
+                   void* out, float* hT, void* scratch, size_t scratch_bytes, int B, int S, int Hq, int Hv,
+                   int gate_dtype, int path, unsigned flags, cudaStream_t stream, bool clear_status);
 // TMA descriptors of q, k ([B,S,Hq,128], 64x64 boxes) and v ([B,S,Hv,128], v_box_cols x 64 boxes).
 int encode_qkv_maps(const Problem& p, void* tq, void* tk, void* tv, int v_box_cols);
 

@@ -21,7 +21,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["gdn_chunk", "gdn_chunk_twolevel", "gdn_chunk_reference", "scan_transfers", "GDN_D", "GDN_CHUNK"]
+__all__ = ["gdn_chunk", "gdn_chunk_host", "gdn_chunk_twolevel", "gdn_chunk_reference", "scan_transfers", "GDN_D", "GDN_CHUNK"]
 
 GDN_D = 128      # head dim (compile-time constant in the kernels)
 GDN_CHUNK = 64   # intra-chunk size (compile-time constant)
@@ -127,6 +127,74 @@ def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, pat
         out [B, S, Hv, D] bf16, and final_state [B, Hv, D, D] fp32 (None when not requested).
     """
     return _forward(q, k, v, g, beta, output_final_state, initial_state, path, bool(use_qk_l2norm_in_kernel))
+
+
+_arena = {}    # (device index, stream slot) -> uint8 device tensor for gdn_chunk_host
+
+
+def gdn_chunk_host(q, k, v, g, beta, output_final_state=True, initial_state=None, out=None, final_state_out=None,
+                   device=None, seg_tokens=0, use_qk_l2norm_in_kernel=False, synchronize=True, arena_slot=0):
+    """gdn_chunk for inputs and results in HOST memory, with the copies pipelined against the kernels.
+
+    q, k, v (bf16), g, beta (bf16 or fp32) and initial_state (fp32) are CPU tensors, contiguous; page-locked
+    tensors (`pin_memory()`) are needed for the overlap.  The sequence is cut into segments; while segment i runs
+    on the GPU the inputs of segment i+1 travel in and the outputs of segment i-1 travel out (C ABI:
+    gdn_chunk_fwd_host_sm100).  Results land in `out` [B,S,Hv,D] bf16 and `final_state_out` [B,Hv,D,D] fp32
+    (pinned CPU tensors, allocated when not given).  With synchronize=False the call returns while copies are
+    still in flight on the current stream: synchronise that stream before reading the results.  Calls that may
+    be in flight at the same time (different streams) must use different `arena_slot` values.
+    """
+    B, S, Hk, Hv = _check_inputs(q, k, v, g, beta)
+    for name, x in (("q", q), ("k", k), ("v", v), ("g", g), ("beta", beta)):
+        if x.is_cuda:
+            raise ValueError(f"{name} is a CUDA tensor: use gdn_chunk for device tensors")
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    q, k, v = (x.contiguous() if x.dtype == torch.bfloat16 else x.to(torch.bfloat16).contiguous() for x in (q, k, v))
+    if g.dtype == torch.bfloat16 and beta.dtype == torch.bfloat16:
+        gate = _lib.GATE_BF16
+        g, beta = g.contiguous(), beta.contiguous()
+    else:
+        g, beta = g.float().contiguous(), beta.float().contiguous()
+        gate = _lib.GATE_F32
+    h0 = None
+    if initial_state is not None:
+        if tuple(initial_state.shape) != (B, Hv, GDN_D, GDN_D):
+            raise ValueError(f"initial_state must be [B,Hv,{GDN_D},{GDN_D}], got {tuple(initial_state.shape)}")
+        h0 = initial_state.to(torch.float32).contiguous()
+    if out is None:
+        out = torch.empty((B, S, Hv, GDN_D), dtype=torch.bfloat16).pin_memory()
+    elif tuple(out.shape) != (B, S, Hv, GDN_D) or out.dtype != torch.bfloat16 or out.is_cuda or not out.is_contiguous():
+        raise ValueError("out must be a contiguous CPU bf16 tensor [B,S,Hv,D]")
+    hT = None
+    if output_final_state:
+        hT = final_state_out
+        if hT is None:
+            hT = torch.empty((B, Hv, GDN_D, GDN_D), dtype=torch.float32).pin_memory()
+        elif tuple(hT.shape) != (B, Hv, GDN_D, GDN_D) or hT.dtype != torch.float32 or hT.is_cuda or not hT.is_contiguous():
+            raise ValueError("final_state_out must be a contiguous CPU fp32 tensor [B,Hv,D,D]")
+    with torch.cuda.device(dev):
+        nbytes = int(lib.gdn_chunk_host_arena_bytes(B, S, Hk, Hv, gate, int(seg_tokens)))
+        key = (dev.index, int(arena_slot))
+        arena = _arena.get(key)
+        if arena is None or arena.numel() < nbytes:
+            arena = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+            _arena[key] = arena
+        stream = torch.cuda.current_stream(dev)
+        st = lib.gdn_chunk_fwd_host_sm100(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+            h0.data_ptr() if h0 is not None else None, out.data_ptr(), hT.data_ptr() if hT is not None else None,
+            arena.data_ptr(), arena.numel(), B, S, Hk, Hv, gate, int(seg_tokens),
+            _lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0, stream.cuda_stream)
+        _lib.check(st, "gdn_chunk_fwd_host_sm100")
+        if synchronize:
+            stream.synchronize()
+            if os.environ.get("GDN_CHUNK_CHECK_STATUS", "0") == "1":
+                import ctypes
+                word = ctypes.c_int(0)
+                if lib.gdn_chunk_read_status(arena.data_ptr(), stream.cuda_stream, ctypes.byref(word)) != _lib.GDN_OK:
+                    raise _lib.GdnLibraryError(f"device status 0x{word.value:x}")
+    return out, hT
 
 
 def scan_transfers(A, Bm, h0=None):

@@ -105,6 +105,28 @@ int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const vo
                            int B, int S, int Hq, int Hv, int gate_dtype, int path, unsigned flags, void* stream);
 
 /*
+ * The forward pass on HOST buffers, pipelined.  q, k, v, g, beta, h0, out, hT are HOST pointers with the
+ * shapes and dtypes of gdn_chunk_fwd_sm100 (page-locked memory is needed for the copies to overlap; pageable
+ * memory works but serialises); `arena` is DEVICE memory of gdn_chunk_host_arena_bytes(...) bytes, 256-byte
+ * aligned, owned by the caller.  The sequence is cut into segments of seg_tokens tokens (a multiple of 64;
+ * 0 = the library picks four segments); the inputs of segment i+1, the kernels of segment i and the
+ * outputs of segment i-1 travel at the same time, each segment starting from the fp32 state the one before
+ * ended with (exact).  Kernels run on `stream`, the copies on two internal streams of the device; the call
+ * returns without waiting and everything enqueued on `stream` afterwards runs after the last output byte has
+ * reached host memory - synchronise `stream` before reading out / hT on the host.  One status word at the
+ * start of the arena collects the bounded-wait reports of all segments (gdn_chunk_read_status(arena, ...)).
+ * Calls that share an arena must be issued on the same stream; calls with different arenas on different
+ * streams overlap each other's copies.  flags as in gdn_chunk_fwd_sm100_ex.
+ * Replaces what a caller of the reference writes around it by hand: `.cuda()` on every input, the operator,
+ * `.cpu()` on the results (the reference's benchmarks create their tensors on the device,
+ * benchmarks/bench_gdn_chunk.py:23-27, and leave the host link out of the picture).
+ */
+size_t gdn_chunk_host_arena_bytes(int B, int S, int Hq, int Hv, int gate_dtype, int seg_tokens);
+int gdn_chunk_fwd_host_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                             const float* h0, void* out, float* hT, void* arena, size_t arena_bytes, int B, int S,
+                             int Hq, int Hv, int gate_dtype, int seg_tokens, unsigned flags, void* stream);
+
+/*
  * Second level of the two-level chunk scan.  A [n_seq][G][128][128] and Bm (same shape), fp32: group g
  * of sequence s maps its incoming state to its outgoing state by S_out = A S_in + Bm.  Writes the
  * state every group starts from into s_in [n_seq][G][128][128] and the state after the last group
