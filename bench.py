@@ -36,7 +36,7 @@ UNIT = "tokens/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one gdn_chain_kernel launch on the default workload (ncu, profiles/)
 CHAIN_DRAM_BYTES_DEFAULT = 361.8e6
-COOP_DRAM_BYTES_DEFAULT = 343.6e6
+COOP_DRAM_BYTES_DEFAULT = 328.7e6
 
 
 def flops_per_token(Hq, Hv, C=64, D=128):
