@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--output-gate", action="store_true",
+                    help="also time the step with the gated RMS normalisation chained behind it (extra key \"with_output_gate\")")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -329,6 +331,35 @@ def main():
         e2e = {"value": modes[best], "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "steps": n_e2e, "api": best, "all": modes}
 
+    # ---- optional: the layer's next step (gated RMS normalisation of O) chained behind the forward pass ----
+    with_gate = None
+    if args.output_gate:
+        from gdn_qsa_sm80_b200 import rmsnorm_gated
+        gen = torch.Generator().manual_seed(args.seed + 1000 + rank)
+        zg = (1.5 * torch.randn(B_local, w.S, w.Hv, 128, generator=gen)).bfloat16().to(dev)
+        wg = torch.ones(128, dtype=torch.bfloat16, device=dev)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            ts = []
+            for _ in range(args.steps):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b))
+            return sorted(ts)[len(ts) // 2]
+
+        o_dev, _ = step()
+        fused_ms = timed(lambda: gdn_chunk(d_in[0], d_in[1], d_in[2], d_in[3], d_in[4], output_final_state=True,
+                                           initial_state=d_in[5], path=args.path, output_gate=(zg, wg)))
+        alone_cold_ms = timed(lambda: rmsnorm_gated(o_dev, zg, wg, out=o_dev))
+        with_gate = {"step_ms_median": fused_ms, "gate_alone_after_l2_flush_ms": alone_cold_ms,
+                     "gate_bytes": 3 * o_dev.numel() * 2}
+
     # ---- the two kernels of a step timed on their own (CUDA events on the launching stream, L2 flushed) ----
     per_kernel = None
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -402,6 +433,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks.summary(),
             "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline}
+    if with_gate is not None:
+        line["with_output_gate"] = with_gate
     if world == 1 and not args.no_cpu_baseline:
         base = cpu_arm(args.workload, args.seed)
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}

@@ -34,6 +34,7 @@ PATH_COOP = 8
 PATH_COOP_CHAIN_ONLY = 9
 PATH_COOP_DEDICATED = 10
 FLAG_QK_L2NORM = 1
+FLAG_GATE_ACTIVATIONS = 2
 
 PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "fused_nv64": PATH_FUSED_NV64, "fused_nv32": PATH_FUSED_NV32,
          "twopass_nv64": PATH_TWOPASS_NV64, "twopass_nv32": PATH_TWOPASS_NV32,
@@ -46,6 +47,8 @@ EXPORTS = (
     "gdn_chunk_fwd_sm100",
     "gdn_chunk_fwd_sm100_ex",
     "gdn_chunk_host_arena_bytes",
+    "gdn_rmsnorm_gated_sm100",
+    "gdn_chunk_fwd_gated_sm100",
     "gdn_chunk_fwd_host_sm100",
     "gdn_chunk_fwd_sm100_noalloc",
     "gdn_chunk_scan_transfers",
@@ -87,6 +90,10 @@ def load() -> ctypes.CDLL:
     lib.gdn_chunk_host_arena_bytes.restype = sz
     lib.gdn_chunk_fwd_host_sm100.argtypes = [vp] * 9 + [sz] + [ci] * 6 + [ctypes.c_uint, vp]
     lib.gdn_chunk_fwd_host_sm100.restype = ci
+    lib.gdn_rmsnorm_gated_sm100.argtypes = [vp, vp, vp, vp, ctypes.c_longlong, ctypes.c_float, vp]
+    lib.gdn_rmsnorm_gated_sm100.restype = ci
+    lib.gdn_chunk_fwd_gated_sm100.argtypes = [vp] * 8 + [ctypes.c_float, vp, vp, vp, sz] + [ci] * 6 + [ctypes.c_uint, vp]
+    lib.gdn_chunk_fwd_gated_sm100.restype = ci
     lib.gdn_chunk_fwd_sm100_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]
     lib.gdn_chunk_fwd_sm100_noalloc.restype = ci
     lib.gdn_chunk_scan_transfers.argtypes = [vp, vp, vp, vp, vp, ci, ci, vp]

@@ -153,15 +153,27 @@ int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const vo
                           flags, static_cast<cudaStream_t>(stream_), true);
 }
 
+int gdn_chunk_fwd_gated_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                              const float* h0, const void* z, const void* weight, float eps, void* out, float* hT,
+                              void* scratch, size_t scratch_bytes, int B, int S, int Hq, int Hv, int gate_dtype,
+                              int path, unsigned flags, void* stream_) {
+    if (!z || !weight || !aligned16(z) || !aligned16(weight)) return GDN_ERR_BAD_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const OutputGate gate{z, weight, eps};
+    return forward_device(q, k, v, g, beta, h0, out, hT, scratch, scratch_bytes, B, S, Hq, Hv, gate_dtype, path, flags,
+                          stream, true, &gate);
+}
+
 }  // extern "C"
 
 namespace gdn {
 int forward_device(const void* q, const void* k, const void* v, const void* g, const void* beta, const float* h0,
                    void* out, float* hT, void* scratch, size_t scratch_bytes, int B, int S, int Hq, int Hv,
-                   int gate_dtype, int path, unsigned flags, cudaStream_t stream, bool clear_status) {
-    if (flags & ~static_cast<unsigned>(GDN_FLAG_QK_L2NORM)) return GDN_ERR_BAD_ARGUMENT;
-    // the first-generation fused kernel has no normalisation; every other path folds it into its factors
-    if ((flags & GDN_FLAG_QK_L2NORM) && (path == GDN_PATH_FUSED_NV64 || path == GDN_PATH_FUSED_NV32))
+                   int gate_dtype, int path, unsigned flags, cudaStream_t stream, bool clear_status,
+                   const OutputGate* gate) {
+    if (flags & ~static_cast<unsigned>(GDN_FLAG_QK_L2NORM | GDN_FLAG_GATE_ACTIVATIONS)) return GDN_ERR_BAD_ARGUMENT;
+    // the first-generation fused kernel has neither option; every other path folds them into its prepare step
+    if (flags != 0 && (path == GDN_PATH_FUSED_NV64 || path == GDN_PATH_FUSED_NV32))
         return GDN_ERR_BAD_ARGUMENT;
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
@@ -197,10 +209,18 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     p.B = B; p.S = S; p.Hq = Hq; p.Hv = Hv;
     p.gate_f32 = gate_dtype == GDN_GATE_F32;
     p.l2norm = (flags & GDN_FLAG_QK_L2NORM) ? 1 : 0;
+    p.gate_act = (flags & GDN_FLAG_GATE_ACTIVATIONS) ? 1 : 0;
+    // the normalisation kernel behind whatever produced `out`
+    auto then_gate = [&](int st) -> int {
+        if (st != GDN_OK || !gate) return st;
+        const long long rows = static_cast<long long>(B) * S * Hv;
+        return launch_rmsnorm_gated(out, gate->z, gate->weight, out, rows, gate->eps, stream) == cudaSuccess ? GDN_OK
+                                                                                                          : GDN_ERR_CUDA;
+    };
 
-    if (path == GDN_PATH_SIMT) return launch_simt(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
-    if (path == GDN_PATH_FUSED_NV64) return launch_fused(p, 64, stream);
-    if (path == GDN_PATH_FUSED_NV32) return launch_fused(p, 32, stream);
+    if (path == GDN_PATH_SIMT) return then_gate(launch_simt(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA);
+    if (path == GDN_PATH_FUSED_NV64) return then_gate(launch_fused(p, 64, stream));
+    if (path == GDN_PATH_FUSED_NV32) return then_gate(launch_fused(p, 32, stream));
     // two-kernel path: "prepare" over all chunks in parallel, then the serial "chain"
     int nv;
     if (path == GDN_PATH_TWOPASS_NV64) nv = 64;
@@ -214,16 +234,16 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     ws.U = reinterpret_cast<__nv_bfloat16*>(base + l.U);
     ws.vec = reinterpret_cast<float*>(base + l.vec);
     if (path == GDN_PATH_COOP_DEDICATED)
-        return launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, false, true);
+        return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, false, true));
     if (path == GDN_PATH_COOP_CHAIN_ONLY)
-        return launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, true);
+        return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, true));
     // few independent sequences: one launch in which a head's four column CTAs share the prepare work
     if (path == GDN_PATH_COOP || (path == GDN_PATH_AUTO && coop_supported(p)))
-        return launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream);
-    if (path == GDN_PATH_CHAIN_ONLY) return launch_chain(p, ws, nv, stream);   // workspace left by an earlier call
+        return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream));
+    if (path == GDN_PATH_CHAIN_ONLY) return then_gate(launch_chain(p, ws, nv, stream));   // workspace left by an earlier call
     const int st = launch_prepare(p, ws, stream);
     if (st != GDN_OK || path == GDN_PATH_PREPARE_ONLY) return st;
-    return launch_chain(p, ws, nv, stream);
+    return then_gate(launch_chain(p, ws, nv, stream));
 }
 }  // namespace gdn
 

@@ -162,7 +162,7 @@ __device__ __forceinline__ void prepare_role(const PrepRes& r, int ptid, const C
     };
     auto load_gates = [&](int b, int hv, int t, float& gv, float& bv) {
         prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(b) * p.S + t * kChunk, hv, p.Hv,
-                                  min(kChunk, p.S - t * kChunk), gv, bv, ctx);
+                                  min(kChunk, p.S - t * kChunk), gv, bv, ctx, p.gate_act != 0);
     };
     // optional cycle accounting by thread 0 of one prepare group, summed over its tiles
     const bool prof_on = p.prof != nullptr && ptid == 0 && prof_cta;
@@ -185,6 +185,7 @@ __device__ __forceinline__ void prepare_role(const PrepRes& r, int ptid, const C
         const size_t tile = (static_cast<size_t>(b) * p.Hv + hv) * NT + t;
         int bn, hvn, tn;
         const bool have_next = sched.get(n + 1, bn, hvn, tn);
+        if (p.gate_act) prep_activate_gates(gv, bv);
         prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, ctx);
         ctx.sync();
         GDN_PHASE(0)

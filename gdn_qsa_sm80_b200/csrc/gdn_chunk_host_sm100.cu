@@ -146,7 +146,7 @@ int gdn_chunk_fwd_host_sm100(const void* q, const void* k, const void* v, const 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
-    if (flags & ~static_cast<unsigned>(GDN_FLAG_QK_L2NORM)) return GDN_ERR_BAD_ARGUMENT;
+    if (flags & ~static_cast<unsigned>(GDN_FLAG_QK_L2NORM | GDN_FLAG_GATE_ACTIVATIONS)) return GDN_ERR_BAD_ARGUMENT;
     if (S > 0 && (!q || !k || !v || !g || !beta || !out)) return GDN_ERR_BAD_ARGUMENT;
     if (!arena || (reinterpret_cast<uintptr_t>(arena) & 255u) ||
         arena_bytes < gdn_chunk_host_arena_bytes(B, S, Hq, Hv, gate_dtype, seg_tokens))

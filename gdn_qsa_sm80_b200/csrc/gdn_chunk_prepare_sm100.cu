@@ -106,7 +106,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     float gv, bv;
     prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(cur.b) * p.S + cur.s0, cur.hv, p.Hv,
-                              min(kChunk, p.S - cur.s0), gv, bv);
+                              min(kChunk, p.S - cur.s0), gv, bv, PrepCtx::whole_cta(), p.gate_act != 0);
     float* As = reinterpret_cast<float*>(sm + PSmem::AS);
     float* Tm = reinterpret_cast<float*>(sm + PSmem::TM);
     float* Yt = reinterpret_cast<float*>(sm + PSmem::YT);
@@ -123,6 +123,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const size_t tile = cur.ws_tile;
         // the previous tile's W/U stores must have finished reading their staging buffers
         if (tid == 0) tma_store_wait_read();
+        if (p.gate_act) prep_activate_gates(gv, bv);
         prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256);
         prep_zero_upper_blocks(Tm);
         __syncthreads();
@@ -240,7 +241,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             nxt = decode(Ln);
             if (tid == 0) issue_loads(nxt);
             prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(nxt.b) * p.S + nxt.s0, nxt.hv, p.Hv,
-                                      min(kChunk, p.S - nxt.s0), gv, bv);
+                                      min(kChunk, p.S - nxt.s0), gv, bv, PrepCtx::whole_cta(), p.gate_act != 0);
         }
 
         // epilogue: W and U (bf16) into swizzled staging tiles, then TMA stores to the workspace

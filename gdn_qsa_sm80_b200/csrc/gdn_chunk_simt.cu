@@ -46,7 +46,12 @@ __global__ void __launch_bounds__(128) gdn_recurrent_simt_kernel(Problem p) {
         const int buf = i & 1;
         ks[buf][c] = k_n;
         qs[buf][c] = q_n * scale;
-        const float vi = v_n, dec = __expf(g_n), bt = b_n;
+        float gt = g_n, bt = b_n;
+        if (p.gate_act) {   // raw gates: g = -softplus(.), beta = sigmoid(.)
+            gt = gt > 20.f ? -gt : -log1pf(__expf(gt));
+            bt = 1.f / (1.f + __expf(-bt));
+        }
+        const float vi = v_n, dec = __expf(gt);
         if (i + 1 < p.S) fetch(i + 1);
         __syncthreads();
         float kv = 0.f, rk = 1.f, rq = 1.f;

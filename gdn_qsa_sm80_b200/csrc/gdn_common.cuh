@@ -26,6 +26,7 @@ struct Problem {
     long long* prof;       // optional: 16 per-phase cycle counters written by CTA (0,0,0); null = off
     int B, S, Hq, Hv;
     int gate_f32;          // 0: g/beta are bf16, 1: fp32
+    int gate_act;          // 1: g and beta hold raw values; the kernels apply g = -softplus(.), beta = sigmoid(.)
     int l2norm;            // 1: q and k are L2-normalised per head vector inside the kernels
 };
 
@@ -94,11 +95,21 @@ inline int encode_tma_bf16(void* tmap_out, const void* base, int rank, const uns
 int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu_store, void* tu_load, int nv);
 // Number of SMs of the current device (cached per device).
 int sm_count();
+cudaError_t launch_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out, long long n_rows,
+                                 float eps, cudaStream_t stream);
 // The forward pass on device buffers (what gdn_chunk_fwd_sm100_ex does).  clear_status = false leaves the status
 // word at the start of `scratch` as it is, so that several launches can share one sticky word.
+// gate != nullptr: the output rows are replaced by rmsnorm_gated(row, z, weight), by the normalisation kernel
+// launched right behind the forward pass.
+struct OutputGate {
+    const void* z;
+    const void* weight;
+    float eps;
+};
 int forward_device(const void* q, const void* k, const void* v, const void* g, const void* beta, const float* h0,
                    void* out, float* hT, void* scratch, size_t scratch_bytes, int B, int S, int Hq, int Hv,
-                   int gate_dtype, int path, unsigned flags, cudaStream_t stream, bool clear_status);
+                   int gate_dtype, int path, unsigned flags, cudaStream_t stream, bool clear_status,
+                   const OutputGate* gate = nullptr);
 // TMA descriptors of q, k ([B,S,Hq,128], 64x64 boxes) and v ([B,S,Hv,128], v_box_cols x 64 boxes).
 int encode_qkv_maps(const Problem& p, void* tq, void* tk, void* tv, int v_box_cols);
 

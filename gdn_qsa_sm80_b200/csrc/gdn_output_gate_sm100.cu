@@ -1,0 +1,85 @@
+// Gated RMS normalisation of the operator's output rows, the step that follows gdn_chunk in the layer:
+//     out[r, :] = y[r, :] * rsqrt(mean(y[r, :]^2) + eps) * weight[:] * silu(z[r, :])        (rows of 128)
+// Same arithmetic as the reference's rmsnorm_gated kernel (csrc/output_gate/output_gate.cu:47-98: fp32 sums,
+// rsqrtf(sum / 128 + 1e-6), silu as z / (1 + exp(-z))) and its test's torch expression
+// (tests/test_output_gate.py:12-16).
+//
+// The work is pure streaming (three 256-byte rows per output row), so the kernel is laid out for HBM: 16 threads
+// own one row (one 16-byte load per thread and tensor), a thread keeps kRowsPerThread rows in flight before it
+// touches any of them, the grid is a multiple of the SM count and strides over the rows.  Run directly after the
+// forward pass and in place (out == y), y is still in the 126 MB L2 for outputs up to that size, so only z is
+// read from and only the result written to HBM.
+#include "../../include/gdn_chunk_sm100.h"
+#include "gdn_common.cuh"
+#include "gdn_gate_device.cuh"
+
+namespace gdn {
+namespace {
+
+constexpr int kGateThreads = 256;
+constexpr int kRowsPerThread = 4;
+constexpr int kGateBlocksPerSm = 4;   // 64 registers per thread; the grid is exactly one resident wave
+
+__global__ void __launch_bounds__(kGateThreads, kGateBlocksPerSm) gdn_rmsnorm_gated_kernel(const uint4* y,   // may alias out
+                                                                         const uint4* __restrict__ z,
+                                                                         const uint4* __restrict__ weight, uint4* out,
+                                                                         long long n_rows, float eps) {
+    const int sub = threadIdx.x & 15;                       // which 8 of the row's 128 columns
+    const long long rows_per_block = kGateThreads / 16;     // 16 rows side by side in a block
+    const long long r_in_block = threadIdx.x >> 4;
+    float w[8];
+    gate_unpack8(weight[sub], w);
+    const long long step = static_cast<long long>(gridDim.x) * rows_per_block;
+    // the loop bound is taken on the warp's first row so that both rows of a warp run the same iterations
+    for (long long r0 = static_cast<long long>(blockIdx.x) * rows_per_block + r_in_block; r0 - (r_in_block & 1) < n_rows;
+         r0 += step * kRowsPerThread) {
+        uint4 yv[kRowsPerThread], zv[kRowsPerThread];
+#pragma unroll
+        for (int u = 0; u < kRowsPerThread; ++u) {
+            const long long r = r0 + u * step;
+            yv[u] = make_uint4(0u, 0u, 0u, 0u);
+            zv[u] = yv[u];
+            if (r < n_rows) {
+                yv[u] = y[r * 16 + sub];
+                zv[u] = __ldcs(z + r * 16 + sub);            // read once: streaming
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kRowsPerThread; ++u) {
+            const long long r = r0 + u * step;               // uniform over the 16 threads of a row
+            // rows past the end hold zeros and are not stored: every lane takes part in the shuffles below,
+            // because the two rows of a warp can fall on either side of the end
+            const uint4 pk = gate_row_slice(yv[u], zv[u], w, eps);
+            if (r < n_rows) out[r * 16 + sub] = pk;
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out, long long n_rows,
+                                 float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return cudaSuccess;
+    const long long rows_per_pass = (kGateThreads / 16) * kRowsPerThread;
+    long long blocks = (n_rows + rows_per_pass - 1) / rows_per_pass;
+    const long long cap = static_cast<long long>(sm_count()) * kGateBlocksPerSm;   // one wave; blocks stride over the rows
+    if (blocks > cap) blocks = cap;
+    gdn_rmsnorm_gated_kernel<<<static_cast<unsigned>(blocks), kGateThreads, 0, stream>>>(
+        static_cast<const uint4*>(y), static_cast<const uint4*>(z), static_cast<const uint4*>(weight),
+        static_cast<uint4*>(out), n_rows, eps);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace gdn
+
+extern "C" int gdn_rmsnorm_gated_sm100(const void* y, const void* z, const void* weight, void* out, long long n_rows,
+                                       float eps, void* stream) {
+    if (n_rows < 0 || (n_rows > 0 && (!y || !z || !weight || !out))) return GDN_ERR_BAD_ARGUMENT;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(z) |
+                           reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out);
+    if (bits & 15u) return GDN_ERR_BAD_ARGUMENT;
+    return gdn::launch_rmsnorm_gated(y, z, weight, out, n_rows, eps, static_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? GDN_OK
+               : GDN_ERR_CUDA;
+}

@@ -47,15 +47,24 @@ __device__ __forceinline__ float prep_load_gate(const void* p, size_t idx) {
 template <bool GATE_F32>
 __device__ __forceinline__ void prep_load_gates(const void* g, const void* beta, size_t tok0, int hv, int Hv,
                                                 int valid, float& gv, float& bv,
-                                                PrepCtx ctx = PrepCtx::whole_cta()) {
+                                                PrepCtx ctx = PrepCtx::whole_cta(), bool raw_gates = false) {
     const int tid = ctx.tid;
-    gv = 0.f;
-    bv = 0.f;
+    // padding: zeros, or (raw gates) the values prep_activate_gates maps to zeros
+    gv = raw_gates ? -INFINITY : 0.f;
+    bv = gv;
     if (tid < valid) {
         const size_t idx = (tok0 + tid) * Hv + hv;
         gv = prep_load_gate<GATE_F32>(g, idx);
         bv = prep_load_gate<GATE_F32>(beta, idx);
     }
+}
+
+// Gate activations inside the kernel: g = -softplus(raw), beta = sigmoid(raw), the way a GDN layer derives its gates
+// (an extension; the reference takes finished gates).  -inf maps to g = 0, beta = 0 (padding).  Applied where the
+// values are consumed, not where they are loaded, so the load stays a tile ahead.
+__device__ __forceinline__ void prep_activate_gates(float& gv, float& bv) {
+    gv = gv > 20.f ? -gv : -log1pf(__expf(gv));
+    bv = 1.f / (1.f + __expf(-bv));
 }
 
 // Gate cumsum over the chunk by warp shuffles (threads 0-63 hold one token each: gv, bv) and the decay tables.

@@ -21,7 +21,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["gdn_chunk", "gdn_chunk_host", "gdn_chunk_twolevel", "gdn_chunk_reference", "scan_transfers", "GDN_D", "GDN_CHUNK"]
+__all__ = ["gdn_chunk", "gdn_chunk_host", "rmsnorm_gated", "gdn_chunk_twolevel", "gdn_chunk_reference", "scan_transfers", "GDN_D", "GDN_CHUNK"]
 
 GDN_D = 128      # head dim (compile-time constant in the kernels)
 GDN_CHUNK = 64   # intra-chunk size (compile-time constant)
@@ -46,6 +46,42 @@ def _check_inputs(q, k, v, g, beta):
     return B, S, Hk, Hv
 
 
+def _check_output_gate(output_gate, out_shape, dev):
+    if len(output_gate) == 2:
+        z, weight = output_gate
+        eps = 1e-6
+    else:
+        z, weight, eps = output_gate
+    if tuple(z.shape) != tuple(out_shape):
+        raise ValueError(f"output_gate z must be {tuple(out_shape)}, got {tuple(z.shape)}")
+    if weight.numel() != GDN_D:
+        raise ValueError(f"output_gate weight must have {GDN_D} elements")
+    z = z.to(device=dev, dtype=torch.bfloat16).contiguous()
+    weight = weight.to(device=dev, dtype=torch.bfloat16).contiguous()
+    return z, weight, float(eps)
+
+
+def rmsnorm_gated(y, z, weight, eps=1e-6, out=None):
+    """out[i] = RMSNorm(y)[i] * weight[i] * silu(z[i]) per 128-wide row: the reference's operator of the same name
+    (gdn_qsa_sm80/output_gate_interface.py:15-27).  y, z: [N, 128] (any leading shape) bf16 CUDA tensors;
+    weight: [128] bf16.  `out` may be y (in place)."""
+    if y.shape != z.shape or y.size(-1) != GDN_D or weight.numel() != GDN_D:
+        raise ValueError(f"y and z must be [..., {GDN_D}] with equal shapes and weight [{GDN_D}]")
+    if not y.is_cuda:
+        raise RuntimeError("rmsnorm_gated needs CUDA tensors (sm_100a); there is no CPU path")
+    y, z, weight = (x.to(torch.bfloat16).contiguous() for x in (y, z, weight))
+    if out is None:
+        out = torch.empty_like(y)
+    elif out.shape != y.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 tensor shaped like y")
+    with torch.cuda.device(y.device):
+        st = _lib.load().gdn_rmsnorm_gated_sm100(y.data_ptr(), z.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                                 y.numel() // GDN_D, float(eps),
+                                                 torch.cuda.current_stream(y.device).cuda_stream)
+    _lib.check(st, "gdn_rmsnorm_gated_sm100")
+    return out
+
+
 def _scratch_for(device, nbytes):
     key = (device.type, device.index)
     buf = _scratch.get(key)
@@ -55,7 +91,12 @@ def _scratch_for(device, nbytes):
     return buf
 
 
-def _forward(q, k, v, g, beta, output_final_state, initial_state, path, l2norm=False):
+def _flags(l2norm, gate_act):
+    return (_lib.FLAG_QK_L2NORM if l2norm else 0) | (_lib.FLAG_GATE_ACTIVATIONS if gate_act else 0)
+
+
+def _forward(q, k, v, g, beta, output_final_state, initial_state, path, l2norm=False, gate_act=False,
+             output_gate=None):
     q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
     B, S, Hk, Hv = _check_inputs(q, k, v, g, beta)
     if not q.is_cuda:
@@ -83,12 +124,21 @@ def _forward(q, k, v, g, beta, output_final_state, initial_state, path, l2norm=F
         nbytes = int(lib.gdn_chunk_scratch_bytes(B, S, Hk, Hv, code))
         scratch = _scratch_for(dev, nbytes)
         stream = torch.cuda.current_stream(dev).cuda_stream
-        st = lib.gdn_chunk_fwd_sm100_ex(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
-            h0.data_ptr() if h0 is not None else None, out.data_ptr(),
-            hT.data_ptr() if hT is not None else None, scratch.data_ptr(), scratch.numel(),
-            B, S, Hk, Hv, gate, code, _lib.FLAG_QK_L2NORM if l2norm else 0, stream)
-        _lib.check(st, "gdn_chunk_fwd_sm100_ex")
+        if output_gate is None:
+            st = lib.gdn_chunk_fwd_sm100_ex(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                h0.data_ptr() if h0 is not None else None, out.data_ptr(),
+                hT.data_ptr() if hT is not None else None, scratch.data_ptr(), scratch.numel(),
+                B, S, Hk, Hv, gate, code, _flags(l2norm, gate_act), stream)
+            _lib.check(st, "gdn_chunk_fwd_sm100_ex")
+        else:
+            z, weight, eps = _check_output_gate(output_gate, (B, S, Hv, GDN_D), dev)
+            st = lib.gdn_chunk_fwd_gated_sm100(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                h0.data_ptr() if h0 is not None else None, z.data_ptr(), weight.data_ptr(), eps, out.data_ptr(),
+                hT.data_ptr() if hT is not None else None, scratch.data_ptr(), scratch.numel(),
+                B, S, Hk, Hv, gate, code, _flags(l2norm, gate_act), stream)
+            _lib.check(st, "gdn_chunk_fwd_gated_sm100")
         if os.environ.get("GDN_CHUNK_CHECK_STATUS", "0") == "1":
             check_device_status(dev)
     return out, hT
@@ -110,7 +160,7 @@ def check_device_status(device=None):
 
 
 def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, path="auto",
-              use_qk_l2norm_in_kernel=False):
+              use_qk_l2norm_in_kernel=False, gate_activations=False, output_gate=None):
     """GDN forward (chunked gated delta rule).
 
     Args:
@@ -122,18 +172,23 @@ def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, pat
         path: "auto", or a key of `_lib.PATHS` to force a kernel.
         use_qk_l2norm_in_kernel: L2-normalise every q and k head vector inside the kernels, the switch of the
             reference's torch definition (reference/gdn_chunk_ref.py:29, :43-45); not on the "fused_*" paths.
+        gate_activations: g and beta are raw projections; the kernels apply g = -softplus(g), beta = sigmoid(beta).
+        output_gate: (z, weight) or (z, weight, eps): `out` becomes rmsnorm_gated(out, z, weight), the layer's next
+            step (reference: output_gate_interface.py:15-27), applied in place right behind the forward pass.
 
     Returns:
         out [B, S, Hv, D] bf16, and final_state [B, Hv, D, D] fp32 (None when not requested).
     """
-    return _forward(q, k, v, g, beta, output_final_state, initial_state, path, bool(use_qk_l2norm_in_kernel))
+    return _forward(q, k, v, g, beta, output_final_state, initial_state, path, bool(use_qk_l2norm_in_kernel),
+                    bool(gate_activations), output_gate)
 
 
 _arena = {}    # (device index, stream slot) -> uint8 device tensor for gdn_chunk_host
 
 
 def gdn_chunk_host(q, k, v, g, beta, output_final_state=True, initial_state=None, out=None, final_state_out=None,
-                   device=None, seg_tokens=0, use_qk_l2norm_in_kernel=False, synchronize=True, arena_slot=0):
+                   device=None, seg_tokens=0, use_qk_l2norm_in_kernel=False, gate_activations=False, synchronize=True,
+                   arena_slot=0):
     """gdn_chunk for inputs and results in HOST memory, with the copies pipelined against the kernels.
 
     q, k, v (bf16), g, beta (bf16 or fp32) and initial_state (fp32) are CPU tensors, contiguous; page-locked
@@ -185,7 +240,7 @@ def gdn_chunk_host(q, k, v, g, beta, output_final_state=True, initial_state=None
             q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
             h0.data_ptr() if h0 is not None else None, out.data_ptr(), hT.data_ptr() if hT is not None else None,
             arena.data_ptr(), arena.numel(), B, S, Hk, Hv, gate, int(seg_tokens),
-            _lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0, stream.cuda_stream)
+            _flags(use_qk_l2norm_in_kernel, gate_activations), stream.cuda_stream)
         _lib.check(st, "gdn_chunk_fwd_host_sm100")
         if synchronize:
             stream.synchronize()

@@ -49,6 +49,7 @@ extern "C" {
 
 /* option bits of gdn_chunk_fwd_sm100_ex */
 #define GDN_FLAG_QK_L2NORM 1u    /* normalise every q and k head vector: x * rsqrt(sum x^2 + 1e-6)    */
+#define GDN_FLAG_GATE_ACTIVATIONS 2u /* g and beta hold raw values: g = -softplus(g), beta = sigmoid(beta) inside */
 
 #define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
 #define GDN_CHUNK 64             /* tokens per chunk                                                */
@@ -97,7 +98,9 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
  * head inside the kernels (fp32, x * rsqrt(sum x^2 + 1e-6)), as use_qk_l2norm_in_kernel does in the
  * reference's torch definition (gdn_qsa_sm80/reference/gdn_chunk_ref.py:15-17, :43-45, :116-118); the
  * reference's CUDA kernels expect normalised inputs and have no such switch, so callers there normalise
- * in a separate pass over q and k.  Not available on the GDN_PATH_FUSED_* paths (GDN_ERR_BAD_ARGUMENT);
+ * in a separate pass over q and k.  GDN_FLAG_GATE_ACTIVATIONS: g and beta are the layer's raw gate
+ * projections and the kernels apply g = -softplus(g), beta = sigmoid(beta) in fp32 where they load them (no
+ * counterpart in the reference, whose callers run these element-wise passes beforehand).  Not available on the GDN_PATH_FUSED_* paths (GDN_ERR_BAD_ARGUMENT);
  * unknown bits are rejected.  flags = 0 is gdn_chunk_fwd_sm100.
  */
 int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const void* g, const void* beta,
@@ -125,6 +128,27 @@ size_t gdn_chunk_host_arena_bytes(int B, int S, int Hq, int Hv, int gate_dtype, 
 int gdn_chunk_fwd_host_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
                              const float* h0, void* out, float* hT, void* arena, size_t arena_bytes, int B, int S,
                              int Hq, int Hv, int gate_dtype, int seg_tokens, unsigned flags, void* stream);
+
+/*
+ * Gated RMS normalisation of rows of 128 bf16 values, the step after gdn_chunk in the layer:
+ *   out[r,:] = y[r,:] * rsqrt(mean(y[r,:]^2) + eps) * weight[:] * silu(z[r,:]),   fp32 arithmetic.
+ * y, z, out [n_rows][128] bf16 (out may be y), weight [128] bf16, all 16-byte aligned.
+ * Replaces the reference's rmsnorm_gated (csrc/output_gate/output_gate.cu:47-98, Python wrapper
+ * gdn_qsa_sm80/output_gate_interface.py:15-27; its eps is the constant 1e-6).
+ */
+int gdn_rmsnorm_gated_sm100(const void* y, const void* z, const void* weight, void* out, long long n_rows,
+                            float eps, void* stream);
+
+/*
+ * gdn_chunk_fwd_sm100_ex followed by the gated normalisation of its output, as one call: `out` receives
+ * rmsnorm_gated(O, z, weight) with O the operator's output (z [B,S,Hv,128] bf16, weight [128] bf16).  The
+ * normalisation runs right behind the forward pass on the same stream and in place, while O is still in L2.
+ * Stands in for the reference's sequence gdn_chunk -> rmsnorm_gated (README.md:127-139 and :184-190).
+ */
+int gdn_chunk_fwd_gated_sm100(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                              const float* h0, const void* z, const void* weight, float eps, void* out, float* hT,
+                              void* scratch, size_t scratch_bytes, int B, int S, int Hq, int Hv, int gate_dtype,
+                              int path, unsigned flags, void* stream);
 
 /*
  * Second level of the two-level chunk scan.  A [n_seq][G][128][128] and Bm (same shape), fp32: group g

@@ -35,6 +35,7 @@ __all__ = [
     "rel_l2",
     "max_abs",
     "l2norm",
+    "rmsnorm_gated",
 ]
 
 
@@ -49,6 +50,15 @@ def expand_qk_heads(x: np.ndarray, hv: int) -> np.ndarray:
 def l2norm(x: np.ndarray, eps: float = 1e-6) -> np.ndarray:
     """x * rsqrt(sum x^2 + eps) over the last axis (gdn_chunk_ref.py:15-17)."""
     return x / np.sqrt((x * x).sum(axis=-1, keepdims=True) + x.dtype.type(eps))
+
+
+def rmsnorm_gated(y, z, weight, eps=1e-6, dtype=np.float32):
+    """RMSNorm(y) * weight * silu(z) over rows of the last axis, in `dtype`; restates the reference's
+    torch_ref_rmsnorm_gated (tests/test_output_gate.py:12-16) and its CUDA kernel's arithmetic
+    (csrc/output_gate/output_gate.cu:64-98)."""
+    y, z, weight = (np.asarray(x, dtype=dtype) for x in (y, z, weight))
+    normed = y / np.sqrt((y * y).mean(axis=-1, keepdims=True) + dtype(eps))
+    return normed * weight * (z / (1 + np.exp(-z)))
 
 
 def _solve_unit_lower(a: np.ndarray, rhs: np.ndarray) -> np.ndarray:

@@ -69,6 +69,14 @@ def test_l2norm_switch_matches_reference(form):
     assert O.rel_l2(out_off, z[f"out_{form}"]) > 0.1
 
 
+def test_rmsnorm_gated_matches_reference_function():
+    z = golden("rmsnorm_gated.npz")
+    out = O.rmsnorm_gated(z["y"], z["z"], z["weight"])
+    assert O.rel_l2(out, z["out_f32"]) < 1e-6
+    # the reference rounds its result to bf16: one bf16 ulp at most between the two
+    assert np.all(np.abs(out - z["out_bf16"]) <= 2.0 ** -8 * np.abs(z["out_f32"]) + 1e-30)
+
+
 def test_cpu_small_workload_matches_reference():
     """The CPU benchmark workload (B1 S512 Hq4 Hv8 fp32 seed 0) regenerated from its seed."""
     z = golden("cpu_small.npz")

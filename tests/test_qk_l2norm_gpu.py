@@ -106,5 +106,23 @@ def test_unknown_flag_bits_are_rejected():
     o = torch.empty_like(x)
     code = lib.gdn_chunk_fwd_sm100_ex(x.data_ptr(), x.data_ptr(), x.data_ptr(), gt.data_ptr(), gt.data_ptr(), None,
                                       o.data_ptr(), None, scratch.data_ptr(), scratch.numel(), 1, 64, 1, 1,
-                                      _lib.GATE_F32, 0, 2, torch.cuda.current_stream().cuda_stream)
+                                      _lib.GATE_F32, 0, 0x80, torch.cuda.current_stream().cuda_stream)
     assert code == _lib.GDN_ERR_BAD_ARGUMENT
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_gate_activations_inside_the_kernel(path):
+    # raw gate projections in, g = -softplus(.), beta = sigmoid(.) applied by the kernels; ragged tail included
+    q, k, v, _, _ = raw_inputs(300, seed=12)
+    gen = torch.Generator().manual_seed(99)
+    g_raw = 2.0 * torch.randn(1, 300, 4, generator=gen)
+    b_raw = 2.0 * torch.randn(1, 300, 4, generator=gen)
+    dev = "cuda"
+    out, st = gdn_chunk(q.to(dev), k.to(dev), v.to(dev), g_raw.to(dev), b_raw.to(dev), path=path,
+                        use_qk_l2norm_in_kernel=True, gate_activations=True)
+    check_device_status()
+    g = -torch.nn.functional.softplus(g_raw)
+    beta = torch.sigmoid(b_raw)
+    ref_o, ref_s = oracle_f32(q, k, v, g, beta, None, l2norm=True)
+    assert_close(out.float().cpu().numpy(), ref_o, f"{path} gate activations out")
+    assert_close(st.cpu().numpy(), ref_s, f"{path} gate activations state")
