@@ -10,6 +10,8 @@ Default workload (B1 S8192 Hq16 Hv32, the configuration the headline metric is q
   * a slice of the result is compared with the CPU oracle run on that slice's prefix only (first 1024 tokens
     of 4 heads).
 Short-batch workload (B16 S2048): production path against the fp32 kernel on a batch slice.
+Long-context (B1 S131072) and throughput (B64 S4096) workloads at full size: production path against the fp32
+recurrent kernel, two-level scan, split-and-chain, batch independence.
 """
 
 import numpy as np
@@ -78,3 +80,59 @@ def test_short_batch_workload_slice_matches_fp32_kernel():
     o2, s2 = gdn_chunk(*[t[sl] for t in d], path="simt")
     assert_close(out[sl].float().cpu().numpy(), o2.float().cpu().numpy(), "O vs fp32 recurrent kernel")
     assert_close(st[sl].cpu().numpy(), s2.cpu().numpy(), "state vs fp32 recurrent kernel")
+
+
+def _device_inputs(workload, seed):
+    """The workload's distributions generated on the GPU (the CPU generator would take minutes at these sizes; no
+    oracle is run on these inputs, only properties between device results)."""
+    from gdn_qsa_sm80_b200.synthetic import WORKLOADS
+    w = WORKLOADS[workload]
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    F = torch.nn.functional
+    rn = lambda *s: torch.randn(*s, generator=gen, device="cuda")
+    q = F.normalize(rn(w.B, w.S, w.Hq, 128), dim=-1).bfloat16()
+    k = F.normalize(rn(w.B, w.S, w.Hq, 128), dim=-1).bfloat16()
+    v = rn(w.B, w.S, w.Hv, 128).bfloat16()
+    g = -F.softplus(rn(w.B, w.S, w.Hv)) * w.gate_scale
+    beta = torch.sigmoid(rn(w.B, w.S, w.Hv))
+    h0 = 0.1 * rn(w.B, w.Hv, 128, 128) if w.h0 != "zeros" else None
+    return w, q, k, v, g, beta, h0
+
+
+def _rel(x, ref):
+    x, ref = x.float(), ref.float()
+    return float((x - ref).norm() / ref.norm().clamp_min(1e-30))
+
+
+def test_long_context_workload_full_size():
+    """B1 S131072: the production path (single launch, 2048 chunks per head) against the fp32 recurrent kernel over the
+    whole sequence, the two-level scan against the serial path, and a split at an odd chunk boundary."""
+    from gdn_qsa_sm80 import gdn_chunk_twolevel
+    w, q, k, v, g, beta, _ = _device_inputs("long_context", 3)
+    out, st = gdn_chunk(q, k, v, g, beta)
+    check_device_status()
+    o2, s2 = gdn_chunk(q, k, v, g, beta, path="simt")
+    assert _rel(out, o2) <= 1e-2 and _rel(st, s2) <= 1e-2
+    assert float((out.float() - o2.float()).abs().max()) <= 2e-2
+    o3, s3, info = gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=256)
+    assert float(info[0]) == 8.0
+    assert _rel(o3, out) <= 3e-3 and _rel(s3, st) <= 3e-3
+    cut = 64 * 777
+    oa, sa = gdn_chunk(q[:, :cut], k[:, :cut], v[:, :cut], g[:, :cut], beta[:, :cut])
+    ob, sb = gdn_chunk(q[:, cut:], k[:, cut:], v[:, cut:], g[:, cut:], beta[:, cut:], initial_state=sa)
+    assert _rel(torch.cat([oa, ob], 1), out) <= 1e-3 and _rel(sb, st) <= 1e-3
+
+
+def test_throughput_workload_full_size():
+    """B64 S4096 (2048 independent sequences, two-kernel path): against the fp32 recurrent kernel on the whole batch,
+    and batch independence: a batch slice run alone gives the same bits as its part of the full run."""
+    w, q, k, v, g, beta, h0 = _device_inputs("throughput", 4)
+    out, st = gdn_chunk(q, k, v, g, beta, initial_state=h0)
+    check_device_status()
+    o2, s2 = gdn_chunk(q, k, v, g, beta, initial_state=h0, path="simt")
+    assert _rel(out, o2) <= 1e-2 and _rel(st, s2) <= 1e-2
+    assert float((out.float() - o2.float()).abs().max()) <= 2e-2
+    del o2, s2
+    sl = slice(40, 44)
+    o3, s3 = gdn_chunk(q[sl], k[sl], v[sl], g[sl], beta[sl], initial_state=h0[sl], path="twopass_nv64")
+    assert torch.equal(o3, out[sl]) and torch.equal(s3, st[sl])
