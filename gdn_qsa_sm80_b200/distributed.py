@@ -24,7 +24,36 @@ from dataclasses import dataclass
 import torch
 import torch.distributed as dist
 
-__all__ = ["Shard", "plan_shards", "shard_inputs", "sequence_parallel_forward", "segment_bounds"]
+__all__ = ["Shard", "plan_shards", "shard_inputs", "sequence_parallel_forward", "segment_bounds",
+           "transfer_is_negligible"]
+
+# exp(x) is below the smallest positive fp32 number (2^-149) for x < -103.3; the margin covers the 128-term sums a
+# state product adds up and the slack of bf16-rounded key norms
+_LOG_UNDERFLOW = -115.0
+
+
+def transfer_is_negligible(k, g, beta, use_qk_l2norm_in_kernel=False):
+    """True when the transfer matrix A of this stretch of tokens (S_out = A S_in + B) is zero to fp32 resolution for
+    every (batch, value head), by a bound that needs no pass over the state:
+
+        A = prod_t exp(g_t) (I - beta_t k_t k_t^T),   ||I - beta k k^T||_2 <= 1  if  0 <= beta ||k||^2 <= 2,
+        so  ||A||_2 <= exp(sum_t g_t)  and every entry of A S_in is below exp(sum_t g_t) ||S_in||.
+
+    With sum_t g_t < -115 that is under 2^-149 times any state norm met in practice: the exact fp32 result of
+    A S_in + B is B.  This is the rigorous form of the reference's approximate "reset" test, which thresholds a
+    measured max |A| (csrc/gdn_chunk/gdn_scan_stage1_reset.cu:17-21, gdn_scan_stage3_reset.cu:1-9).  The check costs
+    two small reductions and one host read; it returns False whenever the premise on beta ||k||^2 fails.
+    """
+    if g.numel() == 0:
+        return False
+    gsum_max = g.float().sum(dim=1).max()
+    if use_qk_l2norm_in_kernel:
+        kk_max = torch.ones((), device=k.device)
+    else:
+        kk_max = k.float().pow(2).sum(dim=-1).max()
+    b = beta.float()
+    ok = (gsum_max < _LOG_UNDERFLOW) & (kk_max * b.max() <= 2.0) & (b.min() >= 0.0) & (g.float().max() <= 0.0)
+    return bool(ok.item())
 
 
 @dataclass(frozen=True)
@@ -81,13 +110,17 @@ def segment_bounds(S: int, world: int, chunk: int = 64) -> list[tuple[int, int]]
 
 
 def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, mode="pipeline", compute=None,
-                              timeout_s: float | None = None):
+                              timeout_s: float | None = None, decay_early_out=True):
     """Forward over THIS rank's contiguous segment of one long sequence.
 
     q..beta: the segment's tensors ([B, S_seg, H, ...]); initial_state: state before the whole sequence
     (only rank 0's is used).  `compute(q, k, v, g, beta, initial_state) -> (out, final_state)` defaults to
     the CUDA operator.  Returns (out_segment, final_state); the final state is the whole sequence's on the
     last rank and this segment's outgoing state elsewhere.
+
+    decay_early_out (mode "scan"): a rank whose segment's transfer matrix is zero to fp32 resolution
+    (`transfer_is_negligible`) skips computing it, and sends its outgoing state - then simply its B_seg - without
+    waiting for the incoming one, which takes that rank out of the serial ripple.  Exact.
     """
     if compute is None:
         from .gdn_chunk_interface import gdn_chunk
@@ -121,15 +154,19 @@ def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, 
     # pass A: this segment's affine transfer, computed by every rank at the same time
     _, b_seg = compute(q, k, v, g, beta, None)
     a_seg = None
-    if rank + 1 < world:     # the last rank never forwards a state, so it needs no transfer matrix
+    forwards = rank + 1 < world     # the last rank never forwards a state, so it needs no transfer matrix
+    skip_a = forwards and decay_early_out and transfer_is_negligible(k, g, beta)
+    if forwards and not skip_a:
         eye = torch.eye(D, dtype=torch.float32, device=dev).expand(shape).contiguous()
         _, a_seg = compute(q, k, torch.zeros_like(v), g, beta, eye)
+    if skip_a:
+        send_state(b_seg)           # A_seg S_in vanishes in fp32: the outgoing state does not depend on the incoming one
     # exchange: ripple the true states down the ranks
     if rank == 0:
         s_in = None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32)
     else:
         s_in = recv_state()
-    if rank + 1 < world:
+    if forwards and not skip_a:
         s_out = b_seg.to(torch.float32) if s_in is None else torch.matmul(a_seg.to(torch.float32), s_in) + b_seg.to(torch.float32)
         send_state(s_out)
     # pass B: the segment from its true incoming state

@@ -271,7 +271,8 @@ def scan_transfers(A, Bm, h0=None):
     return s_in, s_final
 
 
-def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt_eps=1e-2, initial_state=None):
+def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt_eps=1e-2, initial_state=None,
+                       decay_early_out=True):
     """Explicit two-level chunk scan (same name and leading arguments as the reference's
     gdn_chunk_interface.py:53-62).
 
@@ -280,7 +281,14 @@ def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt
     that S_out = A_g S_in + B_g; the scan kernel chains these maps in fp32; pass 2 runs every group from its true
     incoming state and writes the output.  Always exact: eps / frac / gt_eps, which steer the reference's
     approximate reset path, are accepted and ignored.  Returns (out, final_state, info); info holds the number of
-    groups.  S must be a multiple of 64 * group_chunks (otherwise the serial path is used).
+    groups
+    and the number of passes made.  S must be a multiple of 64 * group_chunks (otherwise the serial path is used).
+
+    decay_early_out: when every group's transfer matrix A_g is zero to fp32 resolution by the bound
+    ||A_g|| <= exp(sum of the group's g) (see distributed.transfer_is_negligible; one host read), the pass that
+    computes the A_g is skipped and each group starts from the previous group's B_g: two passes instead of three,
+    same result.  This is the exact counterpart of the reference's approximate reset path
+    (csrc/gdn_chunk/gdn_ops.cu:774-963).
     """
     q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
     B, S, Hk, Hv = _check_inputs(q, k, v, g, beta)
@@ -296,15 +304,26 @@ def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt
 
     qg, kg, vg, gg, bg = (fold(x) for x in (q, k, v, g, beta))
     _, Bm = _forward(qg, kg, vg, gg, bg, True, None, "auto")                       # [B*G, Hv, 128, 128]
-    eye = torch.eye(GDN_D, dtype=torch.float32, device=dev).expand(B * G, Hv, GDN_D, GDN_D).contiguous()
-    _, A = _forward(qg, kg, torch.zeros_like(vg), gg, bg, True, eye, "auto")
-    # [B*G, Hv, ...] -> [B*Hv, G, ...]
-    to_seq = lambda x: x.reshape(B, G, Hv, GDN_D, GDN_D).permute(0, 2, 1, 3, 4).reshape(B * Hv, G, GDN_D, GDN_D)
-    h0 = None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32).reshape(B * Hv, GDN_D, GDN_D)
-    s_in, s_final = scan_transfers(to_seq(A), to_seq(Bm), h0)
-    s_in = s_in.reshape(B, Hv, G, GDN_D, GDN_D).permute(0, 2, 1, 3, 4).reshape(B * G, Hv, GDN_D, GDN_D)
+    from .distributed import transfer_is_negligible
+    if decay_early_out and transfer_is_negligible(kg, gg, bg):
+        # A_g S_in vanishes in fp32 for every group: group j starts from B_{j-1} (the first from the initial state)
+        Bg = Bm.reshape(B, G, Hv, GDN_D, GDN_D)
+        first = (torch.zeros_like(Bg[:, :1]) if initial_state is None
+                 else initial_state.to(device=dev, dtype=torch.float32).reshape(B, 1, Hv, GDN_D, GDN_D))
+        s_in = torch.cat([first, Bg[:, :-1]], dim=1).reshape(B * G, Hv, GDN_D, GDN_D)
+        s_final = Bg[:, -1]
+        passes = 2.0
+    else:
+        eye = torch.eye(GDN_D, dtype=torch.float32, device=dev).expand(B * G, Hv, GDN_D, GDN_D).contiguous()
+        _, A = _forward(qg, kg, torch.zeros_like(vg), gg, bg, True, eye, "auto")
+        # [B*G, Hv, ...] -> [B*Hv, G, ...]
+        to_seq = lambda x: x.reshape(B, G, Hv, GDN_D, GDN_D).permute(0, 2, 1, 3, 4).reshape(B * Hv, G, GDN_D, GDN_D)
+        h0 = None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32).reshape(B * Hv, GDN_D, GDN_D)
+        s_in, s_final = scan_transfers(to_seq(A), to_seq(Bm), h0)
+        s_in = s_in.reshape(B, Hv, G, GDN_D, GDN_D).permute(0, 2, 1, 3, 4).reshape(B * G, Hv, GDN_D, GDN_D)
+        passes = 3.0
     out, _ = _forward(qg, kg, vg, gg, bg, False, s_in, "auto")
-    info = torch.full((1,), float(G), dtype=torch.float32, device=dev)
+    info = torch.tensor([float(G), passes], dtype=torch.float32, device=dev)
     return out.reshape(B, S, Hv, GDN_D), s_final.reshape(B, Hv, GDN_D, GDN_D), info
 
 

@@ -63,18 +63,29 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, mode, S, q_out):
+def _problem(S, g_scale=1.0):
+    q, k, v, g, beta, _ = make_inputs("cpu_small", seed=5, B=1, S=S, Hq=1, Hv=2)
+    h0 = 0.1 * torch.randn(1, 2, 128, 128, generator=torch.Generator().manual_seed(6))
+    return q, k, v, g * g_scale, beta, h0
+
+
+def _worker(rank, world, port, mode, S, q_out, g_scale=1.0):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.set_num_threads(1)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        q, k, v, g, beta, _ = make_inputs("cpu_small", seed=5, B=1, S=S, Hq=1, Hv=2)
-        h0 = 0.1 * torch.randn(1, 2, 128, 128, generator=torch.Generator().manual_seed(6))
+        q, k, v, g, beta, h0 = _problem(S, g_scale)
         lo, hi = segment_bounds(S, world)[rank]
         seg = [t[:, lo:hi] for t in (q, k, v, g, beta)]
-        out, st = sequence_parallel_forward(*seg, initial_state=h0, mode=mode, compute=oracle_compute)
-        q_out.put((rank, out.numpy(), st.numpy()))
+        calls = [0]
+
+        def counted(*a):
+            calls[0] += 1
+            return oracle_compute(*a)
+
+        out, st = sequence_parallel_forward(*seg, initial_state=h0, mode=mode, compute=counted)
+        q_out.put((rank, out.numpy(), st.numpy(), calls[0]))
     finally:
         dist.destroy_process_group()
 
@@ -92,10 +103,49 @@ def test_sequence_parallel_chain_matches_single_process(mode, world, S):
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    q, k, v, g, beta, _ = make_inputs("cpu_small", seed=5, B=1, S=S, Hq=1, Hv=2)
-    h0 = 0.1 * torch.randn(1, 2, 128, 128, generator=torch.Generator().manual_seed(6))
+    q, k, v, g, beta, h0 = _problem(S)
     ref_o, ref_s = oracle_compute(q, k, v, g, beta, h0)
     out = np.concatenate([r[1] for r in results], axis=1)
     tol = 1e-6 if mode == "pipeline" else 2e-5      # the scan mode re-associates the state products (fp32 hop)
     assert O.rel_l2(out, ref_o.numpy()) < tol
     assert O.rel_l2(results[-1][2], ref_s.numpy()) < tol
+    # weak decay: nothing may be skipped - 1 pass per rank in the pipeline, 3 (2 on the last rank) in the scan
+    assert [r[3] for r in results] == ([1] * world if mode == "pipeline" else [3] * (world - 1) + [2])
+
+
+def test_scan_mode_skips_vanishing_transfer_matrices_exactly():
+    """Strong decay (sum of g per segment < -115): exp(sum g) underflows fp32, the forwarding ranks skip the pass
+    that computes their transfer matrix and send B_seg at once; the result is that of the single process."""
+    world, S, g_scale = 3, 384, 6.0
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, "scan", S, q_out, g_scale)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted([q_out.get(timeout=120) for _ in range(world)], key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    q, k, v, g, beta, h0 = _problem(S, g_scale)
+    assert float(g[:, :128].sum(1).max()) < -115
+    ref_o, ref_s = oracle_compute(q, k, v, g, beta, h0)
+    out = np.concatenate([r[1] for r in results], axis=1)
+    assert O.rel_l2(out, ref_o.numpy()) < 1e-6
+    assert O.rel_l2(results[-1][2], ref_s.numpy()) < 1e-6
+    assert [r[3] for r in results] == [2, 2, 2]
+
+
+def test_transfer_bound_premises():
+    from gdn_qsa_sm80_b200.distributed import transfer_is_negligible
+    q, k, v, g, beta, _ = _problem(256, 6.0)
+    assert transfer_is_negligible(k, g, beta)
+    assert not transfer_is_negligible(k, g / 6.0, beta)                 # decay too weak
+    assert not transfer_is_negligible(3.0 * k, g, beta)                 # beta |k|^2 may exceed 2: no norm bound
+    assert transfer_is_negligible(3.0 * k, g, beta, use_qk_l2norm_in_kernel=True)
+    assert not transfer_is_negligible(k, g, beta * 1.5 + 1.0)           # beta outside [0, 1] by far
+    assert not transfer_is_negligible(k, -g, beta)                      # growth instead of decay
+    # the bound itself: the true transfer matrix of such a stretch is zero in fp32
+    eye = torch.eye(128).expand(1, 2, 128, 128).contiguous()
+    _, a = oracle_compute(q, k, torch.zeros_like(v), g, beta, eye)
+    assert float(a.abs().max()) == 0.0

@@ -214,13 +214,32 @@ def test_twolevel_scan_matches_serial_path_and_oracle(workload, group_chunks):
     out, st, info = gdn_chunk_twolevel(q.to(dev), k.to(dev), v.to(dev), g.to(dev), beta.to(dev),
                                        group_chunks=group_chunks, initial_state=h0.to(dev))
     check_device_status()
-    assert float(info[0]) == 4.0
+    assert float(info[0]) == 4.0 and float(info[1]) == 3.0      # weak decay: the transfer matrices are computed
     ro, rs = oracle_f32(q, k, v, g, beta, h0)
     assert_close(out.float().cpu().numpy(), ro, "two-level out vs oracle")
     assert_close(st.cpu().numpy(), rs, "two-level state vs oracle")
     so, ss = run(q, k, v, g, beta, h0, "auto")
     assert_close(out.float().cpu().numpy(), so, "two-level out vs serial")
     assert_close(st.cpu().numpy(), ss, "two-level state vs serial")
+
+
+def test_twolevel_scan_skips_vanishing_transfer_matrices():
+    """Strong decay: every group's sum of g is below the fp32 underflow bound, the pass computing the transfer
+    matrices is skipped (two passes), and the result is that of the three-pass scan and of the oracle."""
+    q, k, v, g, beta, _ = make_inputs("default", seed=71, B=2, S=2048, Hq=2, Hv=4)
+    g = 2.0 * g
+    h0 = 0.1 * torch.randn(2, 4, 128, 128, generator=torch.Generator().manual_seed(72))
+    dev = "cuda"
+    args = [t.to(dev) for t in (q, k, v, g, beta)]
+    out, st, info = gdn_chunk_twolevel(*args, group_chunks=8, initial_state=h0.to(dev))
+    check_device_status()
+    assert float(info[0]) == 4.0 and float(info[1]) == 2.0
+    o3, s3, info3 = gdn_chunk_twolevel(*args, group_chunks=8, initial_state=h0.to(dev), decay_early_out=False)
+    assert float(info3[1]) == 3.0
+    assert torch.equal(out, o3) and torch.equal(st, s3)
+    ro, rs = oracle_f32(q, k, v, g, beta, h0)
+    assert_close(out.float().cpu().numpy(), ro, "two-pass out vs oracle")
+    assert_close(st.cpu().numpy(), rs, "two-pass state vs oracle")
 
 
 @pytest.mark.parametrize("Hq,Hv", [(2, 2), (1, 4), (3, 6)])
