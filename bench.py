@@ -160,6 +160,66 @@ def cpu_arm(workload, seed, min_seconds=10.0, max_reps=12):
             "ms_per_step": med * 1e3}
 
 
+def seq_parallel_arm(args, w, cfg, rank, world, dev):
+    """One sequence cut into `world` contiguous segments (multiples of 64 tokens), one per GPU; rank r's segment is
+    generated from seed + r (the sequence is the concatenation).  A step = the whole sequence-parallel forward."""
+    import torch
+    import torch.distributed as dist
+    from gdn_qsa_sm80_b200 import _lib
+    from gdn_qsa_sm80_b200.distributed import segment_bounds, sequence_parallel_forward
+    from gdn_qsa_sm80_b200.synthetic import make_inputs
+
+    lo, hi = segment_bounds(w.S, world)[rank]
+    q, k, v, g, beta, h0 = make_inputs(w, seed=args.seed + rank, S=hi - lo)
+    d = [t.to(dev) for t in (q, k, v, g, beta)]
+    h0 = None if (h0 is None or rank != 0) else h0.to(dev)
+    mode = "scan" if args.seq_parallel.startswith("scan") else "pipeline"
+    early = args.seq_parallel != "scan_no_early_out"
+
+    def step():
+        return sequence_parallel_forward(*d, initial_state=h0, mode=mode, decay_early_out=early)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    launches0 = _lib.kernel_launches()
+    barrier()
+    total_ms = 0.0
+    with ClockSampler(dev.index) as clocks:
+        for _ in range(args.steps):
+            flush.zero_()
+            barrier()                                     # every step starts on all ranks together
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            step()
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total_ms += float(t.item())
+    launches = _lib.kernel_launches() - launches0
+    ms = total_ms / args.steps
+    tokens = w.B * w.S
+    flops = tokens * (w.Hq * 32768 + w.Hv * 147456)
+    if rank == 0:
+        cfg = dict(cfg, sharding=f"one sequence in {world} contiguous segments, boundary states by send/recv, mode "
+                                 f"{args.seq_parallel}")
+        print(json.dumps({
+            "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks.summary(),
+            "e2e": None, "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": load_peaks()[0]["bf16_tflops"] * world,
+                         "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / (load_peaks()[0]["bf16_tflops"] * world),
+                         "traffic": None, "note": "whole job over all GPUs; algorithmic flops, redundant passes not counted"}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -171,6 +231,9 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--seq-parallel", default=None, choices=["pipeline", "scan", "scan_no_early_out"],
+                    help="with --gpus N > 1: split ONE sequence of the workload into N contiguous segments, one per "
+                         "GPU, boundary states exchanged by send/recv (strong scaling)")
     ap.add_argument("--output-gate", action="store_true",
                     help="also time the step with the gated RMS normalisation chained behind it (extra key \"with_output_gate\")")
     args = ap.parse_args()
@@ -215,6 +278,12 @@ def main():
     if world > 1:
         os.environ.setdefault("NCCL_DEBUG", "WARN")      # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.seq_parallel:
+        seq_parallel_arm(args, w, cfg, rank, world, dev)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- this rank's share of the workload ------------------------------------------------------------
     if args.workload == "default" or w.B < world:

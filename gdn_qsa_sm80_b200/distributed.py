@@ -10,10 +10,13 @@ The reference has no distributed code at all; this module is new.  Two cases:
   rank; the 128x128 fp32 boundary states per value head are passed rank to rank with send/recv (NCCL over
   NVLink on GPUs, gloo in the CPU tests).  Splitting a sequence and chaining states is exact.
   mode="pipeline": rank r waits for its incoming state, runs, sends its final state (serial, 1x work).
-  mode="scan":     every rank first computes its segment's affine transfer S_out = A S_in + B
-                   (B: final state from zeros; A: final state from identity with zero values), then the
-                   states ripple down the ranks (one small matrix product per hop), then every rank runs
-                   its segment from its true incoming state - all ranks busy at once, 3x work per rank.
+  mode="scan":     all ranks busy at once.  Rank 0 runs its segment from the known initial state.  Every other
+                   rank first runs its segment from a zero state (giving B of S_out = A S_in + B).  If the decay
+                   makes the segment forget its incoming state within its first p tokens (a bound checked on the
+                   data), that pass was already right from token p on: the rank sends B at once and recomputes
+                   only the first p tokens when its incoming state arrives.  Otherwise it also computes A (final
+                   state from identity with zero values), the states ripple down the ranks (one small matrix
+                   product per hop), and it reruns the segment from its true incoming state (3x work).
 The received state always lands in this rank's own memory before any kernel reads it.
 """
 
@@ -25,11 +28,25 @@ import torch
 import torch.distributed as dist
 
 __all__ = ["Shard", "plan_shards", "shard_inputs", "sequence_parallel_forward", "segment_bounds",
-           "transfer_is_negligible"]
+           "transfer_is_negligible", "forgetting_horizon"]
 
 # exp(x) is below the smallest positive fp32 number (2^-149) for x < -103.3; the margin covers the 128-term sums a
 # state product adds up and the slack of bf16-rounded key norms
 _LOG_UNDERFLOW = -115.0
+
+
+def _key_norm_sq_max(k):
+    """max over all key vectors of |k|^2 as a 0-dim fp32 tensor on k's device: the library's one-pass kernel for
+    contiguous bf16 CUDA tensors, torch otherwise."""
+    if k.is_cuda and k.dtype == torch.bfloat16 and k.is_contiguous() and k.shape[-1] == 128:
+        from . import _lib
+        out = torch.empty((), dtype=torch.float32, device=k.device)
+        with torch.cuda.device(k.device):
+            st = _lib.load().gdn_key_norm_sq_max_sm100(k.data_ptr(), k.numel() // 128, out.data_ptr(),
+                                                       torch.cuda.current_stream(k.device).cuda_stream)
+        _lib.check(st, "gdn_key_norm_sq_max_sm100")
+        return out
+    return torch.linalg.vector_norm(k, ord=2, dim=-1, dtype=torch.float32).max() ** 2
 
 
 def transfer_is_negligible(k, g, beta, use_qk_l2norm_in_kernel=False):
@@ -46,14 +63,46 @@ def transfer_is_negligible(k, g, beta, use_qk_l2norm_in_kernel=False):
     """
     if g.numel() == 0:
         return False
-    gsum_max = g.float().sum(dim=1).max()
+    gsum_max = g.sum(dim=1, dtype=torch.float32).max()
     if use_qk_l2norm_in_kernel:
         kk_max = torch.ones((), device=k.device)
-    else:
-        kk_max = k.float().pow(2).sum(dim=-1).max()
-    b = beta.float()
-    ok = (gsum_max < _LOG_UNDERFLOW) & (kk_max * b.max() <= 2.0) & (b.min() >= 0.0) & (g.float().max() <= 0.0)
+    else:   # one pass over k, no fp32 copy of it
+        kk_max = _key_norm_sq_max(k)
+    b_lo, b_hi = torch.aminmax(beta)
+    ok = (gsum_max < _LOG_UNDERFLOW) & (kk_max * b_hi.float() <= 2.0) & (b_lo >= 0) & (g.max() <= 0)
     return bool(ok.item())
+
+
+def forgetting_horizon(k, g, beta, chunk: int = 64, keys_are_normalized=False):
+    """Number of leading tokens p (a multiple of `chunk`, or None) after which the state the stretch started from
+    no longer shows in fp32: for every (batch, head) the sum of g over tokens [0, p) is below -115, so by the bound
+    of `transfer_is_negligible` the transfer matrix of [0, t) vanishes for every t >= p.  Outputs at tokens >= p and
+    the final state are then the same whatever the initial state was.  None when there is no such p inside the
+    stretch or the premise (0 <= beta |k|^2 <= 2, g <= 0) fails.  keys_are_normalized=True skips the pass over k
+    (for callers whose keys are L2-normalised by construction, or normalised inside the kernels)."""
+    S = g.shape[1]
+    if g.numel() == 0:
+        return None
+    # sums per chunk first (p is a multiple of the chunk anyway), then a short scan over the chunks
+    nt = (S + chunk - 1) // chunk
+    gf = g.float()
+    if nt * chunk != S:
+        gf = torch.nn.functional.pad(gf, (0, 0, 0, nt * chunk - S))
+    per_chunk = gf.reshape(g.shape[0], nt, chunk, g.shape[2]).sum(dim=2)            # [B, nt, Hv]
+    csum = torch.cumsum(per_chunk, dim=1).amax(dim=(0, 2))            # [nt]: the least-decayed head after every chunk
+    below = csum < _LOG_UNDERFLOW                                       # monotone, because g <= 0
+    first = torch.where(below.any(), below.float().argmax(), torch.full((), nt, device=g.device))
+    if keys_are_normalized:
+        kk_max = torch.ones((), device=k.device)
+    else:
+        kk_max = _key_norm_sq_max(k)
+    b_lo, b_hi = torch.aminmax(beta)
+    ok = (kk_max * b_hi.float() <= 2.0) & (b_lo >= 0) & (g.max() <= 0)
+    first, ok = (int(x) for x in torch.stack([first.float(), ok.float()]).tolist())   # one host read
+    if not ok:
+        return None
+    p = (first + 1) * chunk                                             # chunks [0, first] are needed
+    return p if p < S else None
 
 
 @dataclass(frozen=True)
@@ -110,7 +159,7 @@ def segment_bounds(S: int, world: int, chunk: int = 64) -> list[tuple[int, int]]
 
 
 def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, mode="pipeline", compute=None,
-                              timeout_s: float | None = None, decay_early_out=True):
+                              timeout_s: float | None = None, decay_early_out=True, keys_are_normalized=False):
     """Forward over THIS rank's contiguous segment of one long sequence.
 
     q..beta: the segment's tensors ([B, S_seg, H, ...]); initial_state: state before the whole sequence
@@ -118,9 +167,12 @@ def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, 
     the CUDA operator.  Returns (out_segment, final_state); the final state is the whole sequence's on the
     last rank and this segment's outgoing state elsewhere.
 
-    decay_early_out (mode "scan"): a rank whose segment's transfer matrix is zero to fp32 resolution
-    (`transfer_is_negligible`) skips computing it, and sends its outgoing state - then simply its B_seg - without
-    waiting for the incoming one, which takes that rank out of the serial ripple.  Exact.
+    decay_early_out (mode "scan"): when the decay makes a segment forget its incoming state within its first p
+    tokens (`forgetting_horizon`), the rank's pass from a zero state already yields the right outputs from token p on
+    and the right outgoing state.  It sends that state at once (no transfer matrix, no waiting: the rank leaves the
+    serial ripple) and, once its incoming state has arrived, recomputes only the first p tokens.  A rank then does
+    1 + p / S_seg passes instead of 3, and rank 0, whose incoming state is known from the start, always does one.
+    Exact in fp32.
     """
     if compute is None:
         from .gdn_chunk_interface import gdn_chunk
@@ -151,24 +203,30 @@ def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, 
         return out, s_out
     if mode != "scan":
         raise ValueError(f"unknown mode {mode!r}")
-    # pass A: this segment's affine transfer, computed by every rank at the same time
-    _, b_seg = compute(q, k, v, g, beta, None)
-    a_seg = None
     forwards = rank + 1 < world     # the last rank never forwards a state, so it needs no transfer matrix
-    skip_a = forwards and decay_early_out and transfer_is_negligible(k, g, beta)
-    if forwards and not skip_a:
+    if rank == 0:                   # the incoming state is known: one ordinary pass, its final state goes on
+        s0 = None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32)
+        out, s_fin = compute(q, k, v, g, beta, s0)
+        if forwards:
+            send_state(s_fin)
+        return out, s_fin
+    # pass A: this segment from a zero state (outputs, and B_seg = its final state), on every rank at the same time
+    out, b_seg = compute(q, k, v, g, beta, None)
+    p = forgetting_horizon(k, g, beta, keys_are_normalized=keys_are_normalized) if decay_early_out else None
+    if p is not None:
+        if forwards:
+            send_state(b_seg)       # the outgoing state does not depend on the incoming one
+        s_in = recv_state()
+        head, _ = compute(q[:, :p], k[:, :p], v[:, :p], g[:, :p], beta[:, :p], s_in)
+        out[:, :p] = head           # tokens >= p and the final state are already right
+        return out, b_seg
+    a_seg = None
+    if forwards:
         eye = torch.eye(D, dtype=torch.float32, device=dev).expand(shape).contiguous()
         _, a_seg = compute(q, k, torch.zeros_like(v), g, beta, eye)
-    if skip_a:
-        send_state(b_seg)           # A_seg S_in vanishes in fp32: the outgoing state does not depend on the incoming one
-    # exchange: ripple the true states down the ranks
-    if rank == 0:
-        s_in = None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32)
-    else:
-        s_in = recv_state()
-    if forwards and not skip_a:
-        s_out = b_seg.to(torch.float32) if s_in is None else torch.matmul(a_seg.to(torch.float32), s_in) + b_seg.to(torch.float32)
-        send_state(s_out)
+    s_in = recv_state()             # the true states ripple down the ranks
+    if forwards:
+        send_state(torch.matmul(a_seg.to(torch.float32), s_in) + b_seg.to(torch.float32))
     # pass B: the segment from its true incoming state
     out, s_fin = compute(q, k, v, g, beta, s_in)
     return out, s_fin

@@ -284,10 +284,11 @@ def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt
     groups
     and the number of passes made.  S must be a multiple of 64 * group_chunks (otherwise the serial path is used).
 
-    decay_early_out: when every group's transfer matrix A_g is zero to fp32 resolution by the bound
-    ||A_g|| <= exp(sum of the group's g) (see distributed.transfer_is_negligible; one host read), the pass that
-    computes the A_g is skipped and each group starts from the previous group's B_g: two passes instead of three,
-    same result.  This is the exact counterpart of the reference's approximate reset path
+    decay_early_out: when the decay makes every group forget its incoming state within its first p tokens (the bound
+    ||A|| <= exp(sum of g), see distributed.forgetting_horizon; one host read), pass 1 already gives the right
+    outputs from token p of each group on and the right outgoing states; the A_g are not computed and pass 2 reruns
+    only the first p tokens of every group from the previous group's B_g: 1 + p / (64 * group_chunks) passes
+    instead of three, same result.  This is the exact counterpart of the reference's approximate reset path
     (csrc/gdn_chunk/gdn_ops.cu:774-963).
     """
     q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
@@ -303,16 +304,20 @@ def gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=64, eps=1e-6, frac=1.0, gt
         return x.reshape(B * G, seg, *x.shape[2:])
 
     qg, kg, vg, gg, bg = (fold(x) for x in (q, k, v, g, beta))
-    _, Bm = _forward(qg, kg, vg, gg, bg, True, None, "auto")                       # [B*G, Hv, 128, 128]
-    from .distributed import transfer_is_negligible
-    if decay_early_out and transfer_is_negligible(kg, gg, bg):
-        # A_g S_in vanishes in fp32 for every group: group j starts from B_{j-1} (the first from the initial state)
+    out1, Bm = _forward(qg, kg, vg, gg, bg, True, None, "auto")                    # [B*G, Hv, 128, 128]
+    from .distributed import forgetting_horizon
+    p = forgetting_horizon(kg, gg, bg) if decay_early_out else None
+    if p is not None:
+        # every group has forgotten its incoming state after p tokens: pass 1 is right from there on, and group j
+        # really starts from B_{j-1} (the first from the initial state)
         Bg = Bm.reshape(B, G, Hv, GDN_D, GDN_D)
         first = (torch.zeros_like(Bg[:, :1]) if initial_state is None
                  else initial_state.to(device=dev, dtype=torch.float32).reshape(B, 1, Hv, GDN_D, GDN_D))
         s_in = torch.cat([first, Bg[:, :-1]], dim=1).reshape(B * G, Hv, GDN_D, GDN_D)
-        s_final = Bg[:, -1]
-        passes = 2.0
+        head, _ = _forward(qg[:, :p], kg[:, :p], vg[:, :p], gg[:, :p], bg[:, :p], False, s_in, "auto")
+        out1[:, :p] = head
+        info = torch.tensor([float(G), 1.0 + p / seg], dtype=torch.float32, device=dev)
+        return out1.reshape(B, S, Hv, GDN_D), Bg[:, -1].contiguous(), info
     else:
         eye = torch.eye(GDN_D, dtype=torch.float32, device=dev).expand(B * G, Hv, GDN_D, GDN_D).contiguous()
         _, A = _forward(qg, kg, torch.zeros_like(vg), gg, bg, True, eye, "auto")

@@ -151,6 +151,14 @@ int gdn_chunk_fwd_gated_sm100(const void* q, const void* k, const void* v, const
                               int path, unsigned flags, void* stream);
 
 /*
+ * *out_max (device) = max over the n_rows rows of k [n_rows][128] bf16 of the row's sum of squares, fp32.
+ * Premise check of the exact decay bound that lets the two-level and sequence-parallel drivers skip work
+ * (||I - beta k k^T|| <= 1 needs beta |k|^2 <= 2).  Launches on `stream`, does not wait.  The reference has
+ * no counterpart: its reset test measures max|A| after computing A (csrc/gdn_chunk/gdn_scan_stage3_reset.cu:22-54).
+ */
+int gdn_key_norm_sq_max_sm100(const void* k, long long n_rows, float* out_max, void* stream);
+
+/*
  * Second level of the two-level chunk scan.  A [n_seq][G][128][128] and Bm (same shape), fp32: group g
  * of sequence s maps its incoming state to its outgoing state by S_out = A S_in + Bm.  Writes the
  * state every group starts from into s_in [n_seq][G][128][128] and the state after the last group

@@ -109,13 +109,15 @@ def test_sequence_parallel_chain_matches_single_process(mode, world, S):
     tol = 1e-6 if mode == "pipeline" else 2e-5      # the scan mode re-associates the state products (fp32 hop)
     assert O.rel_l2(out, ref_o.numpy()) < tol
     assert O.rel_l2(results[-1][2], ref_s.numpy()) < tol
-    # weak decay: nothing may be skipped - 1 pass per rank in the pipeline, 3 (2 on the last rank) in the scan
-    assert [r[3] for r in results] == ([1] * world if mode == "pipeline" else [3] * (world - 1) + [2])
+    # weak decay: nothing may be skipped - 1 pass per rank in the pipeline; in the scan 1 on rank 0 (its incoming
+    # state is known), 3 on the ranks in the middle, 2 on the last (it forwards nothing)
+    assert [r[3] for r in results] == ([1] * world if mode == "pipeline" else [1] + [3] * (world - 2) + [2])
 
 
 def test_scan_mode_skips_vanishing_transfer_matrices_exactly():
-    """Strong decay (sum of g per segment < -115): exp(sum g) underflows fp32, the forwarding ranks skip the pass
-    that computes their transfer matrix and send B_seg at once; the result is that of the single process."""
+    """Strong decay: within 64 tokens the sum of g falls below -115 and exp of it underflows fp32, so ranks 1 and 2
+    send the final state of their zero-state pass at once and recompute only their first 64 tokens (the second
+    call of each); the result is that of the single process."""
     world, S, g_scale = 3, 384, 6.0
     ctx = mp.get_context("spawn")
     q_out = ctx.Queue()
@@ -133,7 +135,22 @@ def test_scan_mode_skips_vanishing_transfer_matrices_exactly():
     out = np.concatenate([r[1] for r in results], axis=1)
     assert O.rel_l2(out, ref_o.numpy()) < 1e-6
     assert O.rel_l2(results[-1][2], ref_s.numpy()) < 1e-6
-    assert [r[3] for r in results] == [2, 2, 2]
+    assert [r[3] for r in results] == [1, 2, 2]
+
+
+def test_forgetting_horizon():
+    from gdn_qsa_sm80_b200.distributed import forgetting_horizon
+    q, k, v, g, beta, _ = _problem(256, 6.0)
+    p = forgetting_horizon(k, g, beta)
+    assert p == 64 and float(g[:, :p].sum(1).max()) < -115
+    assert forgetting_horizon(k, g / 6.0, beta) is None                 # never forgotten inside 256 tokens
+    assert forgetting_horizon(3.0 * k, g, beta) is None                 # no norm bound
+    assert forgetting_horizon(3.0 * k, g, beta, keys_are_normalized=True) == 64
+    # what the horizon promises: from token p on, outputs and the final state ignore the initial state
+    h0 = torch.randn(1, 2, 128, 128)
+    o0, s0 = oracle_compute(q, k, v, g, beta, None)
+    o1, s1 = oracle_compute(q, k, v, g, beta, h0)
+    assert torch.equal(o0[:, p:], o1[:, p:]) and torch.equal(s0, s1) and not torch.equal(o0[:, :p], o1[:, :p])
 
 
 def test_transfer_bound_premises():

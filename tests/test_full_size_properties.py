@@ -115,7 +115,7 @@ def test_long_context_workload_full_size():
     assert _rel(out, o2) <= 1e-2 and _rel(st, s2) <= 1e-2
     assert float((out.float() - o2.float()).abs().max()) <= 2e-2
     o3, s3, info = gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=256)
-    assert float(info[0]) == 8.0 and float(info[1]) == 2.0     # 16384-token groups: the transfer matrices vanish
+    assert float(info[0]) == 8.0 and 1.0 < float(info[1]) < 1.3   # 16384-token groups forget their past early
     o4, s4, info4 = gdn_chunk_twolevel(q, k, v, g, beta, group_chunks=256, decay_early_out=False)
     assert float(info4[1]) == 3.0
     assert _rel(o4, o3) <= 1e-6 and _rel(s4, s3) <= 1e-6        # skipping them changes nothing

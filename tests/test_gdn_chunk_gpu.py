@@ -224,8 +224,9 @@ def test_twolevel_scan_matches_serial_path_and_oracle(workload, group_chunks):
 
 
 def test_twolevel_scan_skips_vanishing_transfer_matrices():
-    """Strong decay: every group's sum of g is below the fp32 underflow bound, the pass computing the transfer
-    matrices is skipped (two passes), and the result is that of the three-pass scan and of the oracle."""
+    """Strong decay: every group forgets its incoming state within its first p tokens, so no transfer matrices are
+    computed and only those p tokens are rerun (1 + p/512 passes); the result is that of the three-pass scan and of
+    the oracle."""
     q, k, v, g, beta, _ = make_inputs("default", seed=71, B=2, S=2048, Hq=2, Hv=4)
     g = 2.0 * g
     h0 = 0.1 * torch.randn(2, 4, 128, 128, generator=torch.Generator().manual_seed(72))
@@ -233,10 +234,12 @@ def test_twolevel_scan_skips_vanishing_transfer_matrices():
     args = [t.to(dev) for t in (q, k, v, g, beta)]
     out, st, info = gdn_chunk_twolevel(*args, group_chunks=8, initial_state=h0.to(dev))
     check_device_status()
-    assert float(info[0]) == 4.0 and float(info[1]) == 2.0
+    assert float(info[0]) == 4.0 and 1.0 < float(info[1]) < 2.0
     o3, s3, info3 = gdn_chunk_twolevel(*args, group_chunks=8, initial_state=h0.to(dev), decay_early_out=False)
     assert float(info3[1]) == 3.0
-    assert torch.equal(out, o3) and torch.equal(st, s3)
+    # identical up to the rounding of the fp32 scan's matrix products (which multiply by exact zeros here)
+    assert_close(out.float().cpu().numpy(), o3.float().cpu().numpy(), "early-out vs three passes", rel=1e-5, mabs=1e-5)
+    assert_close(st.cpu().numpy(), s3.cpu().numpy(), "early-out state vs three passes", rel=1e-6, mabs=1e-6)
     ro, rs = oracle_f32(q, k, v, g, beta, h0)
     assert_close(out.float().cpu().numpy(), ro, "two-pass out vs oracle")
     assert_close(st.cpu().numpy(), rs, "two-pass state vs oracle")
