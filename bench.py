@@ -67,8 +67,9 @@ class ClockSampler:
                   "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, index):
+    def __init__(self, index, interval=0.002):
         self.index = index
+        self.interval = interval
         self.sm, self.mx, self.reasons = [], [], set()
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
@@ -115,7 +116,7 @@ class ClockSampler:
                     self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.002 if self._nvml is not None else 0.1)
+            self._stop.wait(self.interval if self._nvml is not None else 0.1)
 
     def __enter__(self):
         self._thread.start()
@@ -184,13 +185,17 @@ def seq_parallel_arm(args, w, cfg, rank, world, dev):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(args.warmup):     # warm-up steps run exactly like timed ones (flush, barrier, step)
+        flush.zero_()
+        barrier()
+        step()
     launches0 = _lib.kernel_launches()
     barrier()
-    total_ms = 0.0
-    with ClockSampler(dev.index) as clocks:
+    total_ms, per_step = 0.0, []
+    # a step here is dozens of small launches from Python: sample the clocks sparsely so that the NVML reads do not
+    # compete with them for the driver
+    with ClockSampler(dev.index, interval=0.01) as clocks:
         for _ in range(args.steps):
             flush.zero_()
             barrier()                                     # every step starts on all ranks together
@@ -203,6 +208,7 @@ def seq_parallel_arm(args, w, cfg, rank, world, dev):
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             total_ms += float(t.item())
+            per_step.append(round(float(t.item()), 4))
     launches = _lib.kernel_launches() - launches0
     ms = total_ms / args.steps
     tokens = w.B * w.S
@@ -214,7 +220,7 @@ def seq_parallel_arm(args, w, cfg, rank, world, dev):
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks.summary(),
-            "e2e": None, "gpu_launches": int(launches),
+            "e2e": None, "gpu_launches": int(launches), "step_ms": per_step,
             "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": load_peaks()[0]["bf16_tflops"] * world,
                          "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / (load_peaks()[0]["bf16_tflops"] * world),
                          "traffic": None, "note": "whole job over all GPUs; algorithmic flops, redundant passes not counted"}}))

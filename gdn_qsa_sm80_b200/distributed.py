@@ -35,6 +35,16 @@ __all__ = ["Shard", "plan_shards", "shard_inputs", "sequence_parallel_forward", 
 _LOG_UNDERFLOW = -115.0
 
 
+_side_streams = {}
+
+
+def _side_stream(dev):
+    key = torch.device(dev).index
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(dev)
+    return _side_streams[key]
+
+
 def _key_norm_sq_max(k):
     """max over all key vectors of |k|^2 as a 0-dim fp32 tensor on k's device: the library's one-pass kernel for
     contiguous bf16 CUDA tensors, torch otherwise."""
@@ -211,8 +221,18 @@ def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, 
             send_state(s_fin)
         return out, s_fin
     # pass A: this segment from a zero state (outputs, and B_seg = its final state), on every rank at the same time
+    inputs_ready = torch.cuda.current_stream(dev).record_event() if v.is_cuda else None
     out, b_seg = compute(q, k, v, g, beta, None)
-    p = forgetting_horizon(k, g, beta, keys_are_normalized=keys_are_normalized) if decay_early_out else None
+    p = None
+    if decay_early_out and v.is_cuda:
+        # the bound's reductions and their host read run on a side stream while pass A, enqueued above, executes
+        # (the side stream waits for the inputs only, not for pass A)
+        side = _side_stream(dev)
+        side.wait_event(inputs_ready)
+        with torch.cuda.stream(side):
+            p = forgetting_horizon(k, g, beta, keys_are_normalized=keys_are_normalized)
+    elif decay_early_out:
+        p = forgetting_horizon(k, g, beta, keys_are_normalized=keys_are_normalized)
     if p is not None:
         if forwards:
             send_state(b_seg)       # the outgoing state does not depend on the incoming one
