@@ -9,7 +9,8 @@ from gdn_qsa_sm80_b200 import (  # noqa: F401
     gdn_chunk_host,
     gdn_chunk_reference,
     gdn_chunk_twolevel,
+    gdn_chunk_varlen,
     rmsnorm_gated,
 )
 
-__all__ = ["rmsnorm_gated", "gdn_chunk", "gdn_chunk_host", "gdn_chunk_twolevel", "gdn_chunk_reference"]
+__all__ = ["rmsnorm_gated", "gdn_chunk_varlen", "gdn_chunk", "gdn_chunk_host", "gdn_chunk_twolevel", "gdn_chunk_reference"]

@@ -7,8 +7,9 @@ from .gdn_chunk_interface import (
     gdn_chunk_host,
     gdn_chunk_reference,
     gdn_chunk_twolevel,
+    gdn_chunk_varlen,
     rmsnorm_gated,
 )
 
 __version__ = "0.1.0"
-__all__ = ["rmsnorm_gated", "gdn_chunk", "gdn_chunk_host", "gdn_chunk_twolevel", "gdn_chunk_reference", "GDN_D", "GDN_CHUNK"]
+__all__ = ["rmsnorm_gated", "gdn_chunk_varlen", "gdn_chunk", "gdn_chunk_host", "gdn_chunk_twolevel", "gdn_chunk_reference", "GDN_D", "GDN_CHUNK"]

@@ -21,7 +21,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["gdn_chunk", "gdn_chunk_host", "rmsnorm_gated", "gdn_chunk_twolevel", "gdn_chunk_reference", "scan_transfers", "GDN_D", "GDN_CHUNK"]
+__all__ = ["gdn_chunk", "gdn_chunk_host", "gdn_chunk_varlen", "rmsnorm_gated", "gdn_chunk_twolevel", "gdn_chunk_reference", "scan_transfers", "GDN_D", "GDN_CHUNK"]
 
 GDN_D = 128      # head dim (compile-time constant in the kernels)
 GDN_CHUNK = 64   # intra-chunk size (compile-time constant)
@@ -83,7 +83,8 @@ def rmsnorm_gated(y, z, weight, eps=1e-6, out=None):
 
 
 def _scratch_for(device, nbytes):
-    key = (device.type, device.index)
+    # one buffer per (device, stream): calls on different streams may overlap on the GPU and must not share scratch
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
@@ -96,7 +97,7 @@ def _flags(l2norm, gate_act):
 
 
 def _forward(q, k, v, g, beta, output_final_state, initial_state, path, l2norm=False, gate_act=False,
-             output_gate=None):
+             output_gate=None, out_buf=None, state_buf=None):
     q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
     B, S, Hk, Hv = _check_inputs(q, k, v, g, beta)
     if not q.is_cuda:
@@ -117,8 +118,11 @@ def _forward(q, k, v, g, beta, output_final_state, initial_state, path, l2norm=F
         if tuple(initial_state.shape) != (B, Hv, GDN_D, GDN_D):
             raise ValueError(f"initial_state must be [B,Hv,{GDN_D},{GDN_D}], got {tuple(initial_state.shape)}")
         h0 = initial_state.to(device=dev, dtype=torch.float32).contiguous()
-    out = torch.empty((B, S, Hv, GDN_D), dtype=torch.bfloat16, device=dev)
-    hT = torch.empty((B, Hv, GDN_D, GDN_D), dtype=torch.float32, device=dev) if output_final_state else None
+    # out_buf / state_buf: contiguous views the results are written into directly (used by the packed-batch driver)
+    out = torch.empty((B, S, Hv, GDN_D), dtype=torch.bfloat16, device=dev) if out_buf is None else out_buf
+    hT = None
+    if output_final_state:
+        hT = torch.empty((B, Hv, GDN_D, GDN_D), dtype=torch.float32, device=dev) if state_buf is None else state_buf
     code = _lib.PATHS[path]
     with torch.cuda.device(dev):
         nbytes = int(lib.gdn_chunk_scratch_bytes(B, S, Hk, Hv, code))
@@ -145,10 +149,13 @@ def _forward(q, k, v, g, beta, output_final_state, initial_state, path, l2norm=F
 
 
 def check_device_status(device=None):
-    """Synchronise and raise if the last kernel on `device` reported a bounded wait that ran out."""
+    """Synchronise the current stream of `device` and raise if the last kernel launched on it reported a bounded wait
+    that ran out."""
     import ctypes
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    buf = _scratch.get((device.type, device.index))
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    buf = _scratch.get((device.index, torch.cuda.current_stream(device).cuda_stream))
     if buf is None:
         return
     word = ctypes.c_int(0)
@@ -250,6 +257,65 @@ def gdn_chunk_host(q, k, v, g, beta, output_final_state=True, initial_state=None
                 if lib.gdn_chunk_read_status(arena.data_ptr(), stream.cuda_stream, ctypes.byref(word)) != _lib.GDN_OK:
                     raise _lib.GdnLibraryError(f"device status 0x{word.value:x}")
     return out, hT
+
+
+_varlen_streams = {}
+
+
+def gdn_chunk_varlen(q, k, v, g, beta, cu_seqlens, output_final_state=True, initial_state=None, n_streams=4, **options):
+    """gdn_chunk over a packed batch of sequences of different lengths.
+
+    q, k: [1, T, Hk, D] (or [T, Hk, D]); v: [1, T, Hv, D]; g, beta: [1, T, Hv]; cu_seqlens: the n_seq + 1 cumulative
+    sequence boundaries 0 = c_0 < c_1 < ... < c_n = T as a list or CPU tensor (a CUDA tensor is read back, which
+    synchronises).  Sequence i is tokens [c_i, c_{i+1}); its slice of every packed tensor is contiguous, so each
+    sequence runs as an ordinary forward pass on a view - no padding, no copies - with the launches spread round-robin
+    over `n_streams` streams that are ordered after, and joined back into, the current stream.  The reference has no
+    variable-length entry; its recurrent torch definition (reference/gdn_chunk_ref.py:103-147) applied per sequence
+    defines the result.  initial_state / returned final state: [n_seq, Hv, D, D]; `options` are gdn_chunk's keywords
+    (path, use_qk_l2norm_in_kernel, gate_activations).
+    Returns (out [1, T, Hv, D] bf16 (or [T, Hv, D] when the inputs had no batch axis), final_state or None).
+    """
+    squeeze = q.dim() == 3
+    if squeeze:
+        q, k, v, g, beta = (x.unsqueeze(0) for x in (q, k, v, g, beta))
+    _, T, Hk, Hv = _check_inputs(q, k, v, g, beta)
+    if q.size(0) != 1:
+        raise ValueError("packed tensors must have batch size 1")
+    cu = cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else list(cu_seqlens)
+    if len(cu) < 2 or cu[0] != 0 or cu[-1] != T or any(b <= a for a, b in zip(cu, cu[1:])):
+        raise ValueError(f"cu_seqlens must rise strictly from 0 to T={T}, got {cu}")
+    n_seq = len(cu) - 1
+    if initial_state is not None and tuple(initial_state.shape) != (n_seq, Hv, GDN_D, GDN_D):
+        raise ValueError(f"initial_state must be [n_seq,Hv,{GDN_D},{GDN_D}], got {tuple(initial_state.shape)}")
+    if not q.is_cuda:
+        raise RuntimeError("gdn_chunk_varlen needs CUDA tensors (sm_100a); there is no CPU path")
+    dev = q.device
+    q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+    out = torch.empty((1, T, Hv, GDN_D), dtype=torch.bfloat16, device=dev)
+    states = torch.empty((n_seq, Hv, GDN_D, GDN_D), dtype=torch.float32, device=dev) if output_final_state else None
+    main = torch.cuda.current_stream(dev)
+    n_streams = max(1, min(int(n_streams), n_seq))
+    streams = _varlen_streams.setdefault(dev.index, [])
+    while len(streams) < n_streams:
+        streams.append(torch.cuda.Stream(dev))
+    ready = main.record_event()
+    for i in range(n_seq):
+        a, b = cu[i], cu[i + 1]
+        s = streams[i % n_streams]
+        if i < n_streams:
+            s.wait_event(ready)
+        with torch.cuda.stream(s):
+            h0 = None if initial_state is None else initial_state[i:i + 1]
+            _forward(q[:, a:b], k[:, a:b], v[:, a:b], g[:, a:b], beta[:, a:b], output_final_state, h0,
+                     options.get("path", "auto"), bool(options.get("use_qk_l2norm_in_kernel", False)),
+                     bool(options.get("gate_activations", False)), None, out[:, a:b],
+                     None if states is None else states[i:i + 1])
+    for s in streams[:n_streams]:
+        main.wait_stream(s)
+    for x in (q, k, v, g, beta, out):      # the side streams read and wrote these: keep the allocator informed
+        for s in streams[:n_streams]:
+            x.record_stream(s)
+    return (out[0] if squeeze else out), states
 
 
 def scan_transfers(A, Bm, h0=None):
