@@ -233,7 +233,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="default", choices=["default", "short_batch", "throughput", "long_context"])
-    ap.add_argument("--path", default="auto", choices=["auto", "simt", "fused_nv64", "fused_nv32", "twopass_nv64", "twopass_nv32", "coop", "coop_dedicated"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "fused_nv64", "fused_nv32", "twopass_nv64", "twopass_nv32", "coop", "coop_dedicated", "decode"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")

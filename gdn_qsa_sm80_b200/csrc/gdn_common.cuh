@@ -94,6 +94,7 @@ inline int encode_tma_bf16(void* tmap_out, const void* base, int rank, const uns
 // column slice.  tu_load may be null.
 int encode_workspace_maps(const Problem& p, const Workspace& ws, void* tw, void* tp, void* tu_store, void* tu_load, int nv);
 // Number of SMs of the current device (cached per device).
+cudaError_t launch_decode(const Problem& p, cudaStream_t stream);
 int sm_count();
 cudaError_t launch_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out, long long n_rows,
                                  float eps, cudaStream_t stream);

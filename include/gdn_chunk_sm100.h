@@ -31,7 +31,7 @@ extern "C" {
 #define GDN_GATE_F32 1
 
 /* execution path */
-#define GDN_PATH_AUTO 0          /* COOP when 4*B*Hv <= #SMs, else prepare + chain kernels (split by B*Hv) */
+#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; COOP when 4*B*Hv <= #SMs; else prepare + chain kernels */
 #define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
 #define GDN_PATH_FUSED_NV64 2    /* single fused tcgen05 kernel, 64 value columns per CTA            */
 #define GDN_PATH_FUSED_NV32 3    /* single fused tcgen05 kernel, 32 value columns per CTA            */
@@ -50,6 +50,9 @@ extern "C" {
 /* option bits of gdn_chunk_fwd_sm100_ex */
 #define GDN_FLAG_QK_L2NORM 1u    /* normalise every q and k head vector: x * rsqrt(sum x^2 + 1e-6)    */
 #define GDN_FLAG_GATE_ACTIVATIONS 2u /* g and beta hold raw values: g = -softplus(g), beta = sigmoid(beta) inside */
+
+#define GDN_PATH_DECODE 11       /* token-by-token fp32 kernel laid out for HBM: one or a few new tokens on top
+                                    of a stored state (exact; time grows with S)                         */
 
 #define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
 #define GDN_CHUNK 64             /* tokens per chunk                                                */

@@ -58,7 +58,7 @@ def test_prepare_outputs(S, workload):
     torch.cuda.synchronize()
     off = (ctypes.c_size_t * 5)()
     assert _lib.load().gdn_chunk_workspace_offsets(B, S, Hq, Hv, off) == 0
-    raw = iface._scratch[(dev.type, torch.cuda.current_device())]
+    raw = iface._scratch[(torch.cuda.current_device(), torch.cuda.current_stream(dev).cuda_stream)]
     NT = (S + 63) // 64
     tiles = B * Hv * NT
     Wg = raw[off[0]:off[0] + tiles * 16384].view(torch.bfloat16).float().cpu().numpy().reshape(B, Hv, NT, 64, 128)

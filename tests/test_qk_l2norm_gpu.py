@@ -15,7 +15,7 @@ from helpers import assert_close, golden, oracle_f32
 
 pytestmark = pytest.mark.gpu
 
-PATHS = ["simt", "twopass_nv64", "twopass_nv32", "coop", "coop_dedicated", "auto"]
+PATHS = ["simt", "twopass_nv64", "twopass_nv32", "coop", "coop_dedicated", "auto", "decode"]
 
 
 def run(q, k, v, g, beta, h0=None, path="auto", l2=True):
