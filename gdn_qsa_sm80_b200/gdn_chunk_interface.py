@@ -269,7 +269,9 @@ def gdn_chunk_varlen(q, k, v, g, beta, cu_seqlens, output_final_state=True, init
     sequence boundaries 0 = c_0 < c_1 < ... < c_n = T as a list or CPU tensor (a CUDA tensor is read back, which
     synchronises).  Sequence i is tokens [c_i, c_{i+1}); its slice of every packed tensor is contiguous, so each
     sequence runs as an ordinary forward pass on a view - no padding, no copies - with the launches spread round-robin
-    over `n_streams` streams that are ordered after, and joined back into, the current stream.  The reference has no
+    over `n_streams` streams that are ordered after, and joined back into, the current stream.  Neighbouring
+    sequences of equal length form a regular batch and share one launch (a packed batch of single tokens is one
+    launch of the decode kernel).  The reference has no
     variable-length entry; its recurrent torch definition (reference/gdn_chunk_ref.py:103-147) applied per sequence
     defines the result.  initial_state / returned final state: [n_seq, Hv, D, D]; `options` are gdn_chunk's keywords
     (path, use_qk_l2norm_in_kernel, gate_activations).
@@ -299,17 +301,26 @@ def gdn_chunk_varlen(q, k, v, g, beta, cu_seqlens, output_final_state=True, init
     while len(streams) < n_streams:
         streams.append(torch.cuda.Stream(dev))
     ready = main.record_event()
+    runs = []                       # (first sequence, number of sequences, length): neighbours of equal length
     for i in range(n_seq):
-        a, b = cu[i], cu[i + 1]
-        s = streams[i % n_streams]
-        if i < n_streams:
+        n = cu[i + 1] - cu[i]
+        if runs and runs[-1][2] == n:
+            runs[-1][1] += 1
+        else:
+            runs.append([i, 1, n])
+    n_streams = min(n_streams, len(runs))
+    for j, (i, cnt, n) in enumerate(runs):
+        a, b = cu[i], cu[i + cnt]
+        s = streams[j % n_streams]
+        if j < n_streams:
             s.wait_event(ready)
+        as_batch = lambda x: x[0, a:b].reshape(cnt, n, *x.shape[2:])      # [1, cnt*n, ...] -> [cnt, n, ...], a view
         with torch.cuda.stream(s):
-            h0 = None if initial_state is None else initial_state[i:i + 1]
-            _forward(q[:, a:b], k[:, a:b], v[:, a:b], g[:, a:b], beta[:, a:b], output_final_state, h0,
+            h0 = None if initial_state is None else initial_state[i:i + cnt]
+            _forward(as_batch(q), as_batch(k), as_batch(v), as_batch(g), as_batch(beta), output_final_state, h0,
                      options.get("path", "auto"), bool(options.get("use_qk_l2norm_in_kernel", False)),
-                     bool(options.get("gate_activations", False)), None, out[:, a:b],
-                     None if states is None else states[i:i + 1])
+                     bool(options.get("gate_activations", False)), None, as_batch(out),
+                     None if states is None else states[i:i + cnt])
     for s in streams[:n_streams]:
         main.wait_stream(s)
     for x in (q, k, v, g, beta, out):      # the side streams read and wrote these: keep the allocator informed

@@ -13,7 +13,7 @@ from helpers import assert_close, oracle_f32
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("lens,n_streams", [([64], 1), ([1, 63, 65, 200, 7], 4), ([300, 300, 1024, 5], 2), ([17] * 9, 3)])
+@pytest.mark.parametrize("lens,n_streams", [([64], 1), ([1, 63, 65, 200, 7], 4), ([300, 300, 1024, 5], 2), ([17] * 9, 3), ([1] * 40 + [2, 2, 3], 4)])
 def test_packed_batch_matches_oracle_per_sequence(lens, n_streams):
     T = sum(lens)
     q, k, v, g, beta, _ = make_inputs("default", seed=T, B=1, S=T, Hq=2, Hv=4)
