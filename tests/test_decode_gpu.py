@@ -50,3 +50,24 @@ def test_decode_without_initial_or_final_state():
     assert st is None
     ro, _ = oracle_f32(q, k, v, g, beta, None, form="recurrent")
     assert O.rel_l2(out.float().cpu().numpy(), ro) < 3e-3
+
+
+def test_decode_updates_the_state_in_place_through_the_c_abi():
+    """h0 and hT may be the same buffer for the decode kernel (a CTA reads its whole state before it writes it)."""
+    from gdn_qsa_sm80_b200 import _lib
+    B, S, Hq, Hv = 4, 1, 2, 4
+    q, k, v, g, beta, _ = make_inputs("default", seed=21, B=B, S=S, Hq=Hq, Hv=Hv)
+    dev = "cuda"
+    d = [t.to(dev).contiguous() for t in (q, k, v, g.float(), beta.float())]
+    h0 = torch.randn(B, Hv, 128, 128, device=dev)
+    ref_o, ref_s = gdn_chunk(*d, initial_state=h0, path="decode")
+    state = h0.clone()
+    out = torch.empty_like(d[2])
+    scratch = torch.empty(256, dtype=torch.uint8, device=dev)
+    st = _lib.load().gdn_chunk_fwd_sm100(d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(),
+                                         d[4].data_ptr(), state.data_ptr(), out.data_ptr(), state.data_ptr(),
+                                         scratch.data_ptr(), 256, B, S, Hq, Hv, _lib.GATE_F32, _lib.PATHS["decode"],
+                                         torch.cuda.current_stream().cuda_stream)
+    assert st == _lib.GDN_OK
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref_o) and torch.equal(state, ref_s)
