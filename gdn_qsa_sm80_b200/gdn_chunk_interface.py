@@ -262,7 +262,8 @@ def gdn_chunk_host(q, k, v, g, beta, output_final_state=True, initial_state=None
 _varlen_streams = {}
 
 
-def gdn_chunk_varlen(q, k, v, g, beta, cu_seqlens, output_final_state=True, initial_state=None, n_streams=4, **options):
+def gdn_chunk_varlen(q, k, v, g, beta, cu_seqlens, output_final_state=True, initial_state=None, n_streams=4,
+                     strategy="auto", **options):
     """gdn_chunk over a packed batch of sequences of different lengths.
 
     q, k: [1, T, Hk, D] (or [T, Hk, D]); v: [1, T, Hv, D]; g, beta: [1, T, Hv]; cu_seqlens: the n_seq + 1 cumulative
@@ -271,7 +272,12 @@ def gdn_chunk_varlen(q, k, v, g, beta, cu_seqlens, output_final_state=True, init
     sequence runs as an ordinary forward pass on a view - no padding, no copies - with the launches spread round-robin
     over `n_streams` streams that are ordered after, and joined back into, the current stream.  Neighbouring
     sequences of equal length form a regular batch and share one launch (a packed batch of single tokens is one
-    launch of the decode kernel).  The reference has no
+    launch of the decode kernel).
+    strategy: "views" as described; "padded" gathers all sequences into one regular batch [n_seq, L_max, ...] whose
+    padding tokens carry g = 0 and beta = 0 (they leave the state untouched and their outputs are dropped, so the
+    result is exact), runs one forward pass and scatters the outputs back - two extra passes over the data, but one
+    launch however many sequences there are; "auto" pads when there are more than 8 launches to make and padding
+    at most doubles the token count.  The reference has no
     variable-length entry; its recurrent torch definition (reference/gdn_chunk_ref.py:103-147) applied per sequence
     defines the result.  initial_state / returned final state: [n_seq, Hv, D, D]; `options` are gdn_chunk's keywords
     (path, use_qk_l2norm_in_kernel, gate_activations).
@@ -300,7 +306,6 @@ def gdn_chunk_varlen(q, k, v, g, beta, cu_seqlens, output_final_state=True, init
     streams = _varlen_streams.setdefault(dev.index, [])
     while len(streams) < n_streams:
         streams.append(torch.cuda.Stream(dev))
-    ready = main.record_event()
     runs = []                       # (first sequence, number of sequences, length): neighbours of equal length
     for i in range(n_seq):
         n = cu[i + 1] - cu[i]
@@ -308,6 +313,28 @@ def gdn_chunk_varlen(q, k, v, g, beta, cu_seqlens, output_final_state=True, init
             runs[-1][1] += 1
         else:
             runs.append([i, 1, n])
+    if strategy not in ("auto", "views", "padded"):
+        raise ValueError(f"unknown strategy {strategy!r}")
+    l_max = max(r[2] for r in runs)
+    if strategy == "padded" or (strategy == "auto" and len(runs) > 8 and n_seq * l_max <= 2 * T):
+        import numpy as np
+        lens = np.diff(np.asarray(cu, dtype=np.int64))
+        pos = np.arange(l_max, dtype=np.int64)[None, :]
+        valid_np = pos < lens[:, None]                                                  # [n_seq, l_max]
+        idx_np = np.minimum(np.asarray(cu[:-1], dtype=np.int64)[:, None] + pos, T - 1)  # token of (sequence, position)
+        idx = torch.from_numpy(idx_np).to(dev)
+        valid = torch.from_numpy(valid_np).to(dev)
+        take = lambda x: x[0][idx]                                                      # [n_seq, l_max, ...]
+        gates = [take(x) * valid.unsqueeze(-1).to(x.dtype) for x in (g, beta)]
+        if options.get("gate_activations", False):    # raw gates: the values the activations map to g = 0, beta = 0
+            gates = [torch.where(valid.unsqueeze(-1), take(x), torch.full((), float("-inf"), dtype=x.dtype, device=dev))
+                     for x in (g, beta)]
+        ob, sb = _forward(take(q), take(k), take(v), gates[0], gates[1], output_final_state, initial_state,
+                          options.get("path", "auto"), bool(options.get("use_qk_l2norm_in_kernel", False)),
+                          bool(options.get("gate_activations", False)))
+        out[0][idx[valid]] = ob[valid]
+        return (out[0] if squeeze else out), sb
+    ready = main.record_event()
     n_streams = min(n_streams, len(runs))
     for j, (i, cnt, n) in enumerate(runs):
         a, b = cu[i], cu[i + cnt]

@@ -73,3 +73,34 @@ def test_calls_on_two_streams_do_not_share_scratch():
         assert torch.equal(o1, ref1) and torch.equal(o2, ref2)
     with torch.cuda.stream(s1):
         check_device_status()
+
+
+@pytest.mark.parametrize("lens", [[150, 130, 164, 101, 177, 200, 133, 164, 164, 190, 108, 120], [3] * 5 + [100] * 4 + [7] * 6])
+@pytest.mark.parametrize("opts", [{}, {"gate_activations": True, "use_qk_l2norm_in_kernel": True}])
+def test_padded_strategy_equals_views_strategy(lens, opts):
+    """Padding tokens carry g = 0 and beta = 0: the padded batch gives the per-sequence results (same parity bar
+    against the oracle; the two strategies may pick different kernels, so they are compared with a tolerance)."""
+    T = sum(lens)
+    q, k, v, g, beta, _ = make_inputs("default", seed=T + 5, B=1, S=T, Hq=2, Hv=4)
+    if opts:
+        gen = torch.Generator().manual_seed(T)
+        g, beta = 1.5 * torch.randn(1, T, 4, generator=gen), 1.5 * torch.randn(1, T, 4, generator=gen)
+    h0 = 0.1 * torch.randn(len(lens), 4, 128, 128, generator=torch.Generator().manual_seed(T + 6))
+    cu = np.concatenate([[0], np.cumsum(lens)]).tolist()
+    dev = "cuda"
+    d = [t.to(dev) for t in (q, k, v, g, beta)]
+    o1, s1 = gdn_chunk_varlen(*d, cu, initial_state=h0.to(dev), strategy="views", **opts)
+    o2, s2 = gdn_chunk_varlen(*d, cu, initial_state=h0.to(dev), strategy="padded", **opts)
+    o3, s3 = gdn_chunk_varlen(*d, cu, initial_state=h0.to(dev), **opts)
+    torch.cuda.synchronize()
+    # auto: many launches and little padding -> padded (first case); three runs of equal lengths -> views (second)
+    same_o, same_s = (o2, s2) if len(set(lens)) > 8 else (o1, s1)
+    assert torch.equal(o3, same_o) and torch.equal(s3, same_s)
+    assert_close(o2.float().cpu().numpy(), o1.float().cpu().numpy(), "padded vs views out", rel=5e-3, mabs=1e-2)
+    assert_close(s2.cpu().numpy(), s1.cpu().numpy(), "padded vs views state", rel=5e-3, mabs=1e-2)
+    g_ref = -torch.nn.functional.softplus(g) if opts else g
+    b_ref = torch.sigmoid(beta) if opts else beta
+    for i, (a, b) in enumerate(zip(cu, cu[1:])):
+        ro, rs = oracle_f32(q[:, a:b], k[:, a:b], v[:, a:b], g_ref[:, a:b], b_ref[:, a:b], h0[i:i + 1], l2norm=bool(opts))
+        assert_close(o2[:, a:b].float().cpu().numpy(), ro, f"sequence {i} out (padded)")
+        assert_close(s2[i:i + 1].cpu().numpy(), rs, f"sequence {i} state (padded)")
