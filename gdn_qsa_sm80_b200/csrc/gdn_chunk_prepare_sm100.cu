@@ -121,8 +121,6 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
     for (; L < num_tiles && ok; L += gridDim.x) {
         const size_t tile = cur.ws_tile;
-        // the previous tile's W/U stores must have finished reading their staging buffers
-        if (tid == 0) tma_store_wait_read();
         if (p.gate_act) prep_activate_gates(gv, bv);
         prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256);
         prep_zero_upper_blocks(Tm);
@@ -148,6 +146,10 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (p.l2norm) prep_l2norm_fold(ps, sm + PSmem::KQ, ws.vec + tile * 256);   // while the UMMAs run
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
+        // the previous tile's W/U stores must have finished reading their staging buffers (the A and T-operand
+        // regions) before the mask epilogue below overwrites the first of them; waited for here rather than at the
+        // top of the loop, the gates, the TMA wait and the first UMMAs have hidden most of that latency
+        if (tid == 0) tma_store_wait_read();
         ok = __syncthreads_and(ok);
         if (!ok) break;
         GDN_PHASE(2)
