@@ -29,20 +29,21 @@
 namespace gdn {
 namespace {
 
+// 71 KB per CTA so that three CTAs share an SM: every buffer is reused as soon as its contents are dead.
 struct PSmem {
-    static constexpr uint32_t KQ = 0;                    // [K;Q]: 2 k-halves x 128 rows x 128 B
-    static constexpr uint32_t VT = KQ + 32768;           // V: 2 column halves x 64 rows x 128 B
-    static constexpr uint32_t TS = VT + 16384;           // [T';T'']: 128 rows x 128 B
-    static constexpr uint32_t AS = TS + 16384;           // A fp32 64 x 68
-    static constexpr uint32_t TM = AS + 17408;           // T fp32 64 x 68
+    static constexpr uint32_t KQ = 0;                    // [K;Q]: 2 k-halves x 128 rows x 128 B; V takes Q's place after Q K^T
+    static constexpr uint32_t AS = KQ + 32768;           // A fp32 64 x 68, then the bf16 operand [T';T''], then the U staging tile
+    static constexpr uint32_t TM = AS + 17408;           // T fp32 64 x 68, then the W staging tile
     static constexpr uint32_t YT = TM + 17408;           // merge temporaries
-    static constexpr uint32_t kBytes = YT + 5120;
+    static constexpr uint32_t kBytes = YT + 5120;        // 72704
     static constexpr uint32_t kDynamic = kBytes + 1024;
 };
-constexpr uint32_t kPrepTmemCols = 256;   // W | U; the raw K K^T / Q K^T accumulator reuses the first 64 columns
+// 128 TMEM columns (three CTAs: 384 of the SM's 512): K K^T / Q K^T in the first 64, then W, then U through all 128
+constexpr uint32_t kPrepTmemCols = 128;
+constexpr int kPrepCtasPerSm = 3;
 
 template <bool GATE_F32>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(128, kPrepCtasPerSm)
 gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_u, Problem p, Workspace ws, int NT, long long num_tiles) {
@@ -72,13 +73,16 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         return x;
     };
     auto issue_loads = [&](const Tile& x) {   // one thread
-        mbar_arrive_expect_tx(&bar_tma, 6 * 8192);
+        mbar_arrive_expect_tx(&bar_tma, 4 * 8192);
         tma_load_4d(sm + PSmem::KQ + 0, &tm_k, &bar_tma, 0, x.hq, x.s0, x.b);        // K, d 0-63   -> rows 0-63
         tma_load_4d(sm + PSmem::KQ + 16384, &tm_k, &bar_tma, 64, x.hq, x.s0, x.b);   // K, d 64-127
         tma_load_4d(sm + PSmem::KQ + 8192, &tm_q, &bar_tma, 0, x.hq, x.s0, x.b);     // Q           -> rows 64-127
         tma_load_4d(sm + PSmem::KQ + 24576, &tm_q, &bar_tma, 64, x.hq, x.s0, x.b);
-        tma_load_4d(sm + PSmem::VT + 0, &tm_v, &bar_tma, 0, x.hv, x.s0, x.b);        // V, dv 0-63
-        tma_load_4d(sm + PSmem::VT + 8192, &tm_v, &bar_tma, 64, x.hv, x.s0, x.b);    // V, dv 64-127
+    };
+    auto issue_v = [&](const Tile& x) {       // one thread, once Q K^T is done: V (two 64-column groups) replaces Q
+        mbar_arrive_expect_tx(&bar_tma, 2 * 8192);
+        tma_load_4d(sm + PSmem::KQ + 8192, &tm_v, &bar_tma, 0, x.hv, x.s0, x.b);
+        tma_load_4d(sm + PSmem::KQ + 24576, &tm_v, &bar_tma, 64, x.hv, x.s0, x.b);
     };
 
     // optional cycle accounting by thread 0 of CTA 0, summed over its tiles (slot 15 counts the tiles)
@@ -123,7 +127,6 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const size_t tile = cur.ws_tile;
         if (p.gate_act) prep_activate_gates(gv, bv);
         prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256);
-        prep_zero_upper_blocks(Tm);
         __syncthreads();
         GDN_PHASE(0)
 
@@ -146,13 +149,17 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (p.l2norm) prep_l2norm_fold(ps, sm + PSmem::KQ, ws.vec + tile * 256);   // while the UMMAs run
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
-        // the previous tile's W/U stores must have finished reading their staging buffers (the A and T-operand
-        // regions) before the mask epilogue below overwrites the first of them; waited for here rather than at the
-        // top of the loop, the gates, the TMA wait and the first UMMAs have hidden most of that latency
-        if (tid == 0) tma_store_wait_read();
+        // the previous tile's W/U stores must have finished reading their staging tiles (the T and A buffers) before
+        // those are zeroed / overwritten below; waited for here rather than at the top of the loop, the gates, the
+        // TMA wait and the first UMMAs have hidden most of that latency.  Q is dead now: V takes its place.
+        if (tid == 0) {
+            tma_store_wait_read();
+            issue_v(cur);
+        }
         ok = __syncthreads_and(ok);
         if (!ok) break;
         GDN_PHASE(2)
+        prep_zero_upper_blocks(Tm);   // the T buffer held the previous tile's W staging tile until the wait above
 
         tc_fence_after_sync();
         {
@@ -207,26 +214,61 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
         {   // [T diag(beta e^gamma) ; T diag(beta)] as one 128-row K-major operand
             const int which = tid >> 6;
-            prep_store_scaled_T_row(Tm, which == 0 ? ps.eg : ps.bet, i, sm + PSmem::TS, which * 64 + i);
+            prep_store_scaled_T_row(Tm, which == 0 ? ps.eg : ps.bet, i, sm + PSmem::AS, which * 64 + i);   // A is dead
         }
         fence_proxy_async_smem();
         __syncthreads();
+        ok = mbar_wait(&bar_tma, ph_tma, p.status, kDevTimeoutTma);   // V has landed
+        ph_tma ^= 1;
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
         GDN_PHASE(5)
 
-        if (tid == 0) {   // W = T' K (lanes 0-63, columns 0-127), U = T'' V (lanes 64-127, columns 128-255)
+        // W = T' K and U = T'' V go through the same 128 TMEM columns one after the other.  Both products use the
+        // stacked operand [T';T''] (M = 128): rows 0-63 of the first are W, rows 64-127 of the second are U.
+        constexpr uint32_t idesc_wu = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_MN);
+        if (tid == 0) {
             tc_fence_after_sync();
-            constexpr uint32_t idesc = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_MN);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-                const uint64_t ad = umma_smem_desc(sm_u32 + PSmem::TS + ks * 32, 16, 1024, SWZ_128B);
+                const uint64_t ad = umma_smem_desc(sm_u32 + PSmem::AS + ks * 32, 16, 1024, SWZ_128B);
                 const uint64_t bk = umma_smem_desc(sm_u32 + PSmem::KQ + ks * 2048, 16384, 1024, SWZ_128B);
-                umma_bf16_ss(tmem, ad, bk, idesc, ks > 0);
+                umma_bf16_ss(tmem, ad, bk, idesc_wu, ks > 0);
             }
+            umma_commit(&bar_mma);
+        }
+        ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
+        ph_mma ^= 1;
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (warp < 2) {   // W rows (lanes 0-63) -> bf16 -> swizzled staging tile in the T buffer (T fp32 is dead)
+            uint32_t r[32];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                tmem_ld_x32(tmem_addr(tmem, lane_base, q4 * 32), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint4 pk;
+                    pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                    pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                    pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                    pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                    *reinterpret_cast<uint4*>(sm + PSmem::TM + (q4 >> 1) * 8192 +
+                                              swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
+                }
+            }
+        }
+        tc_fence_before_sync();
+        __syncthreads();          // W has left the accumulator
+        if (tid == 0) {
+            tc_fence_after_sync();
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-                const uint64_t ad = umma_smem_desc(sm_u32 + PSmem::TS + ks * 32, 16, 1024, SWZ_128B);
-                const uint64_t bv_ = umma_smem_desc(sm_u32 + PSmem::VT + ks * 2048, 8192, 1024, SWZ_128B);
-                umma_bf16_ss(tmem + 128, ad, bv_, idesc, ks > 0);
+                const uint64_t ad = umma_smem_desc(sm_u32 + PSmem::AS + ks * 32, 16, 1024, SWZ_128B);
+                const uint64_t bv_ = umma_smem_desc(sm_u32 + PSmem::KQ + 8192 + ks * 2048, 16384, 1024, SWZ_128B);
+                umma_bf16_ss(tmem, ad, bv_, idesc_wu, ks > 0);
             }
             umma_commit(&bar_mma);
         }
@@ -236,7 +278,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!ok) break;
         GDN_PHASE(6)
 
-        // every tile buffer is free again: start the next tile's loads and gate reads before the epilogue
+        // K, V and the [T';T''] operand are dead: start the next tile's loads and gate reads before the epilogue
         const long long Ln = L + gridDim.x;
         Tile nxt = cur;
         if (Ln < num_tiles) {
@@ -245,42 +287,22 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(nxt.b) * p.S + nxt.s0, nxt.hv, p.Hv,
                                       min(kChunk, p.S - nxt.s0), gv, bv, PrepCtx::whole_cta(), p.gate_act != 0);
         }
-
-        // epilogue: W and U (bf16) into swizzled staging tiles, then TMA stores to the workspace
         tc_fence_after_sync();
-        {
+        if (warp >= 2) {   // U rows (lanes 64-127) -> staging tile in the A buffer (the operand there is dead)
             uint32_t r[32];
-            if (warp < 2) {
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    tmem_ld_x32(tmem_addr(tmem, lane_base, q4 * 32), r);
-                    tmem_ld_wait();
+            for (int q4 = 0; q4 < 4; ++q4) {
+                tmem_ld_x32(tmem_addr(tmem, lane_base, q4 * 32), r);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint4 pk;
-                        pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
-                        pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
-                        pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
-                        pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-                        *reinterpret_cast<uint4*>(sm + PSmem::TS + (q4 >> 1) * 8192 +
-                                                  swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    tmem_ld_x32(tmem_addr(tmem, lane_base, 128 + q4 * 32), r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint4 pk;
-                        pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
-                        pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
-                        pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
-                        pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-                        *reinterpret_cast<uint4*>(sm + PSmem::AS + (q4 >> 1) * 8192 +
-                                                  swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
-                    }
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint4 pk;
+                    pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                    pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                    pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                    pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                    *reinterpret_cast<uint4*>(sm + PSmem::AS + (q4 >> 1) * 8192 +
+                                              swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
                 }
             }
         }
@@ -289,8 +311,8 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         __syncthreads();
         if (tid == 0) {
             const int row0 = static_cast<int>(tile * kChunk);
-            tma_store_2d(&tm_w, sm + PSmem::TS, 0, row0);
-            tma_store_2d(&tm_w, sm + PSmem::TS + 8192, 64, row0);
+            tma_store_2d(&tm_w, sm + PSmem::TM, 0, row0);
+            tma_store_2d(&tm_w, sm + PSmem::TM + 8192, 64, row0);
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) tma_store_2d(&tm_u, sm + PSmem::AS + h2 * 8192, h2 * 64, row0);
             tma_store_commit();
@@ -318,7 +340,7 @@ int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream) {
     if (encode_workspace_maps(p, ws, &tw, &tp, &tu, nullptr, 64)) return GDN_ERR_DRIVER;
     const int NT = (p.S + kChunk - 1) / kChunk;
     const long long tiles = static_cast<long long>(p.B) * p.Hv * NT;
-    const long long max_ctas = 2ll * sm_count();
+    const long long max_ctas = static_cast<long long>(kPrepCtasPerSm) * sm_count();
     const unsigned grid = static_cast<unsigned>(tiles < max_ctas ? tiles : max_ctas);
     auto go = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PSmem::kDynamic) != cudaSuccess)
