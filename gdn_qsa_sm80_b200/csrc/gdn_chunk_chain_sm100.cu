@@ -12,10 +12,11 @@
 // (csrc/gdn_chunk/gdn_kernel.cu:1027-1224) with mma.sync and a bf16 state; here the products are
 // tcgen05 UMMAs with fp32 accumulators in TMEM and the state stays fp32.
 //
-// Roles (192 threads): warps 0-3 own the four TMEM lane quadrants and do all epilogues; warp 2's
-// first lane issues the UMMAs of the critical path (D3, D5); warp 5's first lane issues D4, which
-// nothing on the critical path waits for; warp 4's first lane is the TMA producer that keeps a ring
-// of STAGES chunks (K, [Q;W], P, U slice, per-token factors) in flight.  Only D3 -> v_new -> D5 ->
+// Roles: G = NV / 32 groups of four epilogue warps (warps 0 .. 4G-1; warp w works on TMEM lane quadrant w % 4 and on
+// the 32 columns [32 (w / 4), +32) of the slice, so an epilogue costs the same whatever NV is); warp 2's first lane
+// issues the UMMAs of the critical path (D3, D5); warp 4G is the TMA producer that keeps a ring of STAGES chunks
+// (K, [Q;W], P, U slice, per-token factors) in flight; warp 4G+1's first lane issues D4, which nothing on the
+// critical path waits for.  192 threads at NV = 32, 320 at NV = 64.  Only D3 -> v_new -> D5 ->
 // state sits on the critical path: the output epilogue of chunk t-1 runs on warps 0-1 while
 // warps 2-3 turn W S into v_new for chunk t, and accumulators are double-buffered so the next D3
 // never waits for an output epilogue.  (A UMMA with N <= 64 occupies the tensor pipe for about 40
@@ -61,21 +62,22 @@ constexpr int kDevTimeoutChainKV = 0x204;
 constexpr int kDevTimeoutChainPV = 0x205;
 constexpr int kDevTimeoutChainVN = 0x206;
 
+// 32 fp32 values -> bf16 -> columns [32 cg, 32 cg + 32) of row `row` of a swizzled tile with NV columns
 template <int NV>
-__device__ __forceinline__ void store_row_bf16(uint8_t* tile, uint32_t row, const float* x) {
+__device__ __forceinline__ void store_row_bf16(uint8_t* tile, uint32_t row, const float* x, int cg) {
 #pragma unroll
-    for (int ch = 0; ch < NV / 8; ++ch) {
+    for (int ch = 0; ch < 4; ++ch) {
         uint4 pk;
         pk.x = pack_bf16x2(x[8 * ch + 0], x[8 * ch + 1]);
         pk.y = pack_bf16x2(x[8 * ch + 2], x[8 * ch + 3]);
         pk.z = pack_bf16x2(x[8 * ch + 4], x[8 * ch + 5]);
         pk.w = pack_bf16x2(x[8 * ch + 6], x[8 * ch + 7]);
-        *reinterpret_cast<uint4*>(tile + swz_chunk_offset<NV * 2>(row, ch)) = pk;
+        *reinterpret_cast<uint4*>(tile + swz_chunk_offset<NV * 2>(row, cg * 4 + ch)) = pk;
     }
 }
 
 template <int NV, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__((NV / 32 * 4 + 2) * 32, 1)
 gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_p,
                  const __grid_constant__ CUtensorMap tm_u, Problem p, Workspace ws) {
@@ -127,7 +129,9 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t tmem = tmem_slot;
     volatile int* abortp = &abort_flag;
 
-    if (warp == 4) {
+    constexpr int kGroups = NV / 32;               // epilogue warp groups, 32 columns each
+    constexpr int kEpiWarps = 4 * kGroups;
+    if (warp == kEpiWarps) {
         // ------------------------------- TMA producer -----------------------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_w);
@@ -152,7 +156,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 bulk_load_1d(st + L::VEC, ws.vec + (tile0 + t) * 256, 1024, &bar_full[s]);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kEpiWarps + 1) {
         // ------------------------------- off-critical-path UMMA issuer: D4 = P v_new -----------------
         if (lane == 0) {
             constexpr uint32_t idesc_pv = umma_idesc_bf16(128, NV, MAJOR_K, MAJOR_MN);
@@ -173,17 +177,20 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     } else {
         // ------------------------------- chain warps ---------------------------------------------------
-        const uint32_t lane_base = static_cast<uint32_t>(warp) * 32u;
-        const bool issuer = (tid == 64);
-        const int i = tid & 63;           // token row handled in the v_new / output epilogues
-        float st[NV];
-        const size_t st_off = ((static_cast<size_t>(b) * p.Hv + hv) * kD + tid) * kD + dv0;
+        const int quad = warp & 3, cg = warp >> 2;     // TMEM lane quadrant; column group of the slice
+        const int row = quad * 32 + lane;              // state row (dk) this thread owns: 0..127
+        const uint32_t lane_base = static_cast<uint32_t>(quad) * 32u;
+        const uint32_t col0 = static_cast<uint32_t>(cg) * 32u;
+        const bool issuer = (tid == 64);               // group 0, quadrant 2
+        const int i = row & 63;           // token row handled in the v_new / output epilogues
+        float st[32];
+        const size_t st_off = ((static_cast<size_t>(b) * p.Hv + hv) * kD + row) * kD + dv0 + col0;
 #pragma unroll
-        for (int c = 0; c < NV; c += 4) {
+        for (int c = 0; c < 32; c += 4) {
             const float4 x = p.h0 ? *reinterpret_cast<const float4*>(p.h0 + st_off + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             st[c] = x.x; st[c + 1] = x.y; st[c + 2] = x.z; st[c + 3] = x.w;
         }
-        store_row_bf16<NV>(sm + L::SB, tid, st);
+        store_row_bf16<NV>(sm + L::SB, row, st, cg);
         fence_proxy_async_smem();
 
         // per-token factors of the current chunk, read from the stage before its D3 is issued
@@ -191,7 +198,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         auto load_factors = [&](int t) {
             const float* vec = reinterpret_cast<const float*>(sm + (t % STAGES) * L::kStage + L::VEC);
             f_tok_prev = f_tok;
-            f_tok = (warp < 2) ? vec[kChunk + i] : vec[i];     // warps 0-1: scale e^gamma_i ; warps 2-3: e^{gamma_C-gamma_i}
+            f_tok = (quad < 2) ? vec[kChunk + i] : vec[i];     // quadrants 0-1: scale e^gamma_i ; 2-3: e^{gamma_C-gamma_i}
             dC = vec[2 * kChunk];
         };
         const uint64_t sb_desc0 = umma_smem_desc(sm_u32 + L::SB, 16384, 8 * L::kRowBytes, L::kSwz);
@@ -212,13 +219,12 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         auto out_epilogue = [&](int t, float qf) {   // rows of chunk t: O = qf * (Q S) + P v_new
             const int s = t * kChunk + i;
             uint32_t a[32], c2[32];
-#pragma unroll
-            for (int part = 0; part < NV / 32; ++part) {
-                tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + part * 32), a);
-                tmem_ld_x32(tmem_addr(tmem, lane_base, kColPV + (t & 1) * NV + part * 32), c2);
+            {
+                tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + col0), a);
+                tmem_ld_x32(tmem_addr(tmem, lane_base, kColPV + (t & 1) * NV + col0), c2);
                 tmem_ld_wait();
                 if (s < p.S) {
-                    __nv_bfloat16* dst = p.out + ((static_cast<size_t>(b) * p.S + s) * p.Hv + hv) * kD + dv0 + part * 32;
+                    __nv_bfloat16* dst = p.out + ((static_cast<size_t>(b) * p.S + s) * p.Hv + hv) * kD + dv0 + col0;
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) {
                         uint4 pk;
@@ -250,49 +256,48 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         bool ok = mbar_wait_abortable(&bar_full[0], 0, p.status, kDevTimeoutChainFull, abortp);
         if (ok) load_factors(0);
         tc_fence_before_sync();
-        named_bar_sync(2, 128);
+        named_bar_sync(2, 128 * kGroups);
         if (issuer && ok) issue_d3(0);
 
         if (prof_on) prof_t = clock64();
         for (int t = 0; t < NT; ++t) {
             const int s = t % STAGES;
             uint8_t* stg = sm + s * L::kStage;
-            if (warp >= 2) {
+            if (quad >= 2) {
                 // ---- v_new = U - W S, and its decay-scaled copy -------------------------------------------
+                float x[32], y[32];
+                // U does not depend on the state: fetch it while D3 is still in flight
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    const uint4 uv = *reinterpret_cast<const uint4*>(stg + L::UB + swz_chunk_offset<NV * 2>(i, cg * 4 + ch));
+                    const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {     // bf16 pair -> two fp32
+                        x[8 * ch + 2 * e] = __uint_as_float(uw[e] << 16);
+                        x[8 * ch + 2 * e + 1] = __uint_as_float(uw[e] & 0xffff0000u);
+                    }
+                }
                 ok = mbar_wait_abortable(&bar_d3, t & 1, p.status, kDevTimeoutChainD3, abortp) && ok;
                 tc_fence_after_sync();
                 GDN_PHASE(0)
-                uint32_t w[32];
-                float x[NV], y[NV];
-#pragma unroll
-                for (int part = 0; part < NV / 32; ++part) {
-                    tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + part * 32), w);
-                    float u[32];
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        const uint4 uv = *reinterpret_cast<const uint4*>(stg + L::UB + swz_chunk_offset<NV * 2>(i, part * 4 + ch));
-                        const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {     // bf16 pair -> two fp32
-                            u[8 * ch + 2 * e] = __uint_as_float(uw[e] << 16);
-                            u[8 * ch + 2 * e + 1] = __uint_as_float(uw[e] & 0xffff0000u);
-                        }
-                    }
+                {
+                    uint32_t w[32];
+                    tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + col0), w);
                     tmem_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
-                        const float vn = u[c] - __uint_as_float(w[c]);
-                        x[part * 32 + c] = vn;
-                        y[part * 32 + c] = vn * f_tok;
+                        const float vn = x[c] - __uint_as_float(w[c]);
+                        x[c] = vn;
+                        y[c] = vn * f_tok;
                     }
                 }
                 if (t > 0)   // D4 of the previous chunk must have finished reading v_new
                     ok = mbar_wait_abortable(&bar_pv[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, kDevTimeoutChainPV, abortp) && ok;
-                store_row_bf16<NV>(sm + L::VN, i, x);
-                store_row_bf16<NV>(sm + L::VS, i, y);
+                store_row_bf16<NV>(sm + L::VN, i, x, cg);
+                store_row_bf16<NV>(sm + L::VS, i, y, cg);
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
-                named_bar_sync(1, 64);
+                named_bar_sync(1, 64 * kGroups);
                 GDN_PHASE(1)
                 if (issuer && ok) {
                     constexpr uint32_t idesc_kv = umma_idesc_bf16(128, NV, MAJOR_MN, MAJOR_MN);
@@ -319,14 +324,11 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             GDN_PHASE(3)
             {
                 uint32_t r[32];
+                tmem_ld_x32(tmem_addr(tmem, lane_base, kColKV + col0), r);
+                tmem_ld_wait();
 #pragma unroll
-                for (int part = 0; part < NV / 32; ++part) {
-                    tmem_ld_x32(tmem_addr(tmem, lane_base, kColKV + part * 32), r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) st[part * 32 + c] = fmaf(dC, st[part * 32 + c], __uint_as_float(r[c]));
-                }
-                store_row_bf16<NV>(sm + L::SB, tid, st);
+                for (int c = 0; c < 32; ++c) st[c] = fmaf(dC, st[c], __uint_as_float(r[c]));
+                store_row_bf16<NV>(sm + L::SB, row, st, cg);
             }
             fence_proxy_async_smem();
             if (t + 1 < NT) {
@@ -337,7 +339,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 f_tok_prev = f_tok;
             }
             tc_fence_before_sync();
-            named_bar_sync(2, 128);
+            named_bar_sync(2, 128 * kGroups);
             GDN_PHASE(4)
             if (issuer && ok && t + 1 < NT) issue_d3(t + 1);
             GDN_PHASE(5)
@@ -345,14 +347,14 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #undef GDN_PHASE
         if (prof_on)
             for (int n = 0; n < 6; ++n) p.prof[8 + n] = prof_acc[n];
-        if (warp < 2 && NT > 0) {   // output rows of the last chunk
+        if (quad < 2 && NT > 0) {   // output rows of the last chunk
             ok = mbar_wait_abortable(&bar_pv[(NT - 1) & 1], ((NT - 1) >> 1) & 1, p.status, kDevTimeoutChainPV, abortp) && ok;
             tc_fence_after_sync();
             out_epilogue(NT - 1, f_tok_prev);
         }
         if (ok && p.hT) {
 #pragma unroll
-            for (int c = 0; c < NV; c += 4)
+            for (int c = 0; c < 32; c += 4)
                 *reinterpret_cast<float4*>(p.hT + st_off + c) = make_float4(st[c], st[c + 1], st[c + 2], st[c + 3]);
         }
     }
@@ -375,7 +377,7 @@ int launch_chain_nv(const Problem& p, const Workspace& ws, cudaStream_t stream) 
     auto kernel = gdn_chain_kernel<NV, STAGES>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess)
         return GDN_ERR_CUDA;
-    const dim3 grid(kD / NV, p.Hv, p.B), block(192);
+    const dim3 grid(kD / NV, p.Hv, p.B), block((NV / 32 * 4 + 2) * 32);
     kernel<<<grid, block, L::kDynamic, stream>>>(tq, tk, tw, tp, tu, p, ws);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
