@@ -15,7 +15,8 @@
 //   DEDICATED = false  NV = 32.  Every CTA is a chain CTA (4 per head) plus one prepare group that prepares every
 //                      fourth chunk of its own head.  12 warps: 0-3 chain epilogues (warp 2 lane 0 issues D3/D5),
 //                      4 TMA producer, 5 issues D4, 6 publisher, 8-11 prepare group.  Needs 4*B*Hv <= #SMs.
-//   DEDICATED = true   NV = 64.  CTAs [0, n_chain) are chain CTAs (2 per head, warps 0-5 as above); the remaining
+//   DEDICATED = true   NV = 64.  CTAs [0, n_chain) are chain CTAs (2 per head: warps 0-7 epilogues in two groups of
+//                      32 columns, 8 TMA producer, 9 issues D4); the remaining
 //                      CTAs hold two prepare groups each (warps 0-3 and 4-7, publishers on warps 8 and 9) and walk
 //                      the tiles chunk-major (every head's chunk 0, then chunk 1, ...), so the chain shares its SM
 //                      with nobody.  Needs 2*B*Hv plus a few CTAs <= #SMs.
@@ -87,16 +88,17 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int* status, volatile
     }
 }
 
+// 32 fp32 values -> bf16 -> columns [32 cg, 32 cg + 32) of row `row` of a swizzled tile with NV columns
 template <int NV>
-__device__ __forceinline__ void store_row_bf16(uint8_t* tile, uint32_t row, const float* x) {
+__device__ __forceinline__ void store_row_bf16(uint8_t* tile, uint32_t row, const float* x, int cg) {
 #pragma unroll
-    for (int ch = 0; ch < NV / 8; ++ch) {
+    for (int ch = 0; ch < 4; ++ch) {
         uint4 pk;
         pk.x = pack_bf16x2(x[8 * ch + 0], x[8 * ch + 1]);
         pk.y = pack_bf16x2(x[8 * ch + 2], x[8 * ch + 3]);
         pk.z = pack_bf16x2(x[8 * ch + 4], x[8 * ch + 5]);
         pk.w = pack_bf16x2(x[8 * ch + 6], x[8 * ch + 7]);
-        *reinterpret_cast<uint4*>(tile + swz_chunk_offset<NV * 2>(row, ch)) = pk;
+        *reinterpret_cast<uint4*>(tile + swz_chunk_offset<NV * 2>(row, cg * 4 + ch)) = pk;
     }
 }
 
@@ -364,8 +366,9 @@ __device__ __forceinline__ void publisher_role(const PrepRes& r, const CUtensorM
 }
 
 // ------------------------------------------------------------------------------------------------------
-// chain roles of one CTA: warps 0-3 epilogues (+ warp 2 lane 0 issues D3 / D5), warp 4 lane 0 TMA producer,
-// warp 5 lane 0 issues D4.  `sm` is the CTA's (1024-byte aligned) dynamic shared memory, chain region first.
+// chain roles of one CTA: G = NV / 32 groups of four epilogue warps (warps 0 .. 4G-1; warp w works on TMEM lane
+// quadrant w % 4 and on columns [32 (w / 4), +32) of the slice; warp 2 lane 0 issues D3 / D5), warp 4G lane 0 TMA
+// producer, warp 4G+1 lane 0 issues D4.  `sm` is the CTA's (1024-byte aligned) dynamic shared memory, chain region first.
 // ------------------------------------------------------------------------------------------------------
 struct ChainBars {
     uint64_t *full, *empty;   // [STAGES] each
@@ -386,7 +389,8 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
     const int NT = (p.S + kChunk - 1) / kChunk;
     const size_t tile0 = (static_cast<size_t>(b) * p.Hv + hv) * NT;
 
-    if (warp == 4) {
+    constexpr int kGroups = NV / 32, kEpiWarps = 4 * kGroups;
+    if (warp == kEpiWarps) {
         if (lane != 0) return;
         // ------------------------------- TMA producer ------------------------------------------------------
         for (int t = 0; t < NT; ++t) {
@@ -413,7 +417,7 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
         }
         return;
     }
-    if (warp == 5) {
+    if (warp == kEpiWarps + 1) {
         if (lane != 0) return;
         // ------------------------------- D4 = P v_new, off the critical path ---------------------------------
         constexpr uint32_t idesc_pv = umma_idesc_bf16(128, NV, MAJOR_K, MAJOR_MN);
@@ -434,25 +438,28 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
         }
         return;
     }
-    // ------------------------------- chain warps 0-3 -----------------------------------------------------------
-    const uint32_t lane_base = static_cast<uint32_t>(warp) * 32u;
-    const bool issuer = (tid == 64);
-    const int i = tid & 63;
-    float st[NV];
-    const size_t st_off = ((static_cast<size_t>(b) * p.Hv + hv) * kD + tid) * kD + dv0;
+    // ------------------------------- epilogue warps -----------------------------------------------------------
+    const int quad = warp & 3, cg = warp >> 2;          // TMEM lane quadrant; column group of the slice
+    const int row = quad * 32 + lane;                   // state row (dk) this thread owns: 0..127
+    const uint32_t lane_base = static_cast<uint32_t>(quad) * 32u;
+    const uint32_t col0 = static_cast<uint32_t>(cg) * 32u;
+    const bool issuer = (tid == 64);                    // group 0, quadrant 2
+    const int i = row & 63;
+    float st[32];
+    const size_t st_off = ((static_cast<size_t>(b) * p.Hv + hv) * kD + row) * kD + dv0 + col0;
 #pragma unroll
-    for (int c = 0; c < NV; c += 4) {
+    for (int c = 0; c < 32; c += 4) {
         const float4 x = p.h0 ? *reinterpret_cast<const float4*>(p.h0 + st_off + c) : make_float4(0.f, 0.f, 0.f, 0.f);
         st[c] = x.x; st[c + 1] = x.y; st[c + 2] = x.z; st[c + 3] = x.w;
     }
-    store_row_bf16<NV>(sm + L::SB, tid, st);
+    store_row_bf16<NV>(sm + L::SB, row, st, cg);
     fence_proxy_async_smem();
 
     float f_tok = 0.f, f_tok_prev = 0.f, dC = 0.f;
     auto load_factors = [&](int t) {
         const float* vec = reinterpret_cast<const float*>(sm + (t % STAGES) * L::kStage + L::VEC);
         f_tok_prev = f_tok;
-        f_tok = (warp < 2) ? vec[kChunk + i] : vec[i];     // warps 0-1: scale e^gamma_i ; warps 2-3: e^{gamma_C-gamma_i}
+        f_tok = (quad < 2) ? vec[kChunk + i] : vec[i];     // quadrants 0-1: scale e^gamma_i ; 2-3: e^{gamma_C-gamma_i}
         dC = vec[2 * kChunk];
     };
     const uint64_t sb_desc0 = umma_smem_desc(sm_u32 + L::SB, 16384, 8 * L::kRowBytes, L::kSwz);
@@ -470,13 +477,12 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
     auto out_epilogue = [&](int t, float qf) {   // rows of chunk t: O = qf * (Q S) + P v_new
         const int s = t * kChunk + i;
         uint32_t a[32], c2[32];
-#pragma unroll
-        for (int part = 0; part < NV / 32; ++part) {
-            tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + part * 32), a);
-            tmem_ld_x32(tmem_addr(tmem, lane_base, kColPV + (t & 1) * NV + part * 32), c2);
+        {
+            tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + col0), a);
+            tmem_ld_x32(tmem_addr(tmem, lane_base, kColPV + (t & 1) * NV + col0), c2);
             tmem_ld_wait();
             if (s < p.S) {
-                __nv_bfloat16* dst = p.out + ((static_cast<size_t>(b) * p.S + s) * p.Hv + hv) * kD + dv0 + part * 32;
+                __nv_bfloat16* dst = p.out + ((static_cast<size_t>(b) * p.S + s) * p.Hv + hv) * kD + dv0 + col0;
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     float o[8];
@@ -504,20 +510,20 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
     bool ok = mbar_wait_abortable(&cb.full[0], 0, p.status, kTimeoutFull, abortp);
     if (ok) load_factors(0);
     tc_fence_before_sync();
-    named_bar_sync(2, 128);
+    named_bar_sync(2, 128 * kGroups);
     if (issuer && ok) issue_d3(0);
 
     if (cprof) ct = clock64();
     for (int t = 0; t < NT; ++t) {
         const int s = t % STAGES;
         uint8_t* stg = sm + s * L::kStage;
-        if (warp >= 2) {
+        if (quad >= 2) {
             // ---- v_new = U - W S, and its decay-scaled copy ---------------------------------------------------
-            float u[NV];
+            float u[32];
             // U does not depend on the state: fetch it while D3 is still in flight
 #pragma unroll
-            for (int ch = 0; ch < NV / 8; ++ch) {
-                const uint4 uv = *reinterpret_cast<const uint4*>(stg + L::UB + swz_chunk_offset<NV * 2>(i, ch));
+            for (int ch = 0; ch < 4; ++ch) {
+                const uint4 uv = *reinterpret_cast<const uint4*>(stg + L::UB + swz_chunk_offset<NV * 2>(i, cg * 4 + ch));
                 const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {     // bf16 pair -> two fp32
@@ -528,26 +534,25 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
             ok = mbar_wait_abortable(cb.d3, t & 1, p.status, kTimeoutD3, abortp) && ok;
             tc_fence_after_sync();
             GDN_CPHASE(0)
-            float y[NV];
-#pragma unroll
-            for (int part = 0; part < NV / 32; ++part) {
+            float y[32];
+            {
                 uint32_t w[32];
-                tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + part * 32), w);
+                tmem_ld_x32(tmem_addr(tmem, lane_base, kColD3 + (t & 1) * NV + col0), w);
                 tmem_ld_wait();
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    const float vn = u[part * 32 + c] - __uint_as_float(w[c]);
-                    u[part * 32 + c] = vn;
-                    y[part * 32 + c] = vn * f_tok;
+                    const float vn = u[c] - __uint_as_float(w[c]);
+                    u[c] = vn;
+                    y[c] = vn * f_tok;
                 }
             }
             if (t > 1)   // v_new is double-buffered: only D4 of chunk t-2 must have finished reading this buffer
                 ok = mbar_wait_abortable(&cb.pv[t & 1], ((t - 2) >> 1) & 1, p.status, kTimeoutPV, abortp) && ok;
-            store_row_bf16<NV>(sm + L::VN + (t & 1) * 64 * L::kRowBytes, i, u);
-            store_row_bf16<NV>(sm + L::VS, i, y);
+            store_row_bf16<NV>(sm + L::VN + (t & 1) * 64 * L::kRowBytes, i, u, cg);
+            store_row_bf16<NV>(sm + L::VS, i, y, cg);
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            named_bar_sync(1, 64);
+            named_bar_sync(1, 64 * kGroups);
             GDN_CPHASE(1)
             if (issuer && ok) {
                 constexpr uint32_t idesc_kv = umma_idesc_bf16(128, NV, MAJOR_MN, MAJOR_MN);
@@ -573,15 +578,14 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
             mbar_arrive(cb.vn);          // D5 is complete: warp 5 may issue D4 without delaying the critical path
         }
         GDN_CPHASE(3)
-#pragma unroll
-        for (int part = 0; part < NV / 32; ++part) {
+        {
             uint32_t r[32];
-            tmem_ld_x32(tmem_addr(tmem, lane_base, kColKV + part * 32), r);
+            tmem_ld_x32(tmem_addr(tmem, lane_base, kColKV + col0), r);
             tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) st[part * 32 + c] = fmaf(dC, st[part * 32 + c], __uint_as_float(r[c]));
+            for (int c = 0; c < 32; ++c) st[c] = fmaf(dC, st[c], __uint_as_float(r[c]));
         }
-        store_row_bf16<NV>(sm + L::SB, tid, st);
+        store_row_bf16<NV>(sm + L::SB, row, st, cg);
         fence_proxy_async_smem();
         GDN_CPHASE(4)
         if (t + 1 < NT) {
@@ -592,7 +596,7 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
             f_tok_prev = f_tok;
         }
         tc_fence_before_sync();
-        named_bar_sync(2, 128);
+        named_bar_sync(2, 128 * kGroups);
         GDN_CPHASE(5)
         if (issuer && ok && t + 1 < NT) issue_d3(t + 1);
         GDN_CPHASE(6)
@@ -600,14 +604,14 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
 #undef GDN_CPHASE
     if (cprof)
         for (int n = 0; n < 7; ++n) p.prof[8 + n] = cacc[n];
-    if (warp < 2 && NT > 0) {   // output rows of the last chunk
+    if (quad < 2 && NT > 0) {   // output rows of the last chunk
         ok = mbar_wait_abortable(&cb.pv[(NT - 1) & 1], ((NT - 1) >> 1) & 1, p.status, kTimeoutPV, abortp) && ok;
         tc_fence_after_sync();
         out_epilogue(NT - 1, f_tok_prev);
     }
     if (ok && p.hT) {
 #pragma unroll
-        for (int c = 0; c < NV; c += 4)
+        for (int c = 0; c < 32; c += 4)
             *reinterpret_cast<float4*>(p.hT + st_off + c) = make_float4(st[c], st[c + 1], st[c + 2], st[c + 3]);
     }
 }
@@ -679,7 +683,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     if (!DEDICATED) {
         // every CTA: chain roles on warps 0-5, publisher on warp 6, one prepare group on warps 8-11
-        if (warp < 6) {
+        if (warp < 4 * (NV / 32) + 2) {
             ChainBars cb{bar_full, bar_empty, &bar_d3, &bar_kv, &bar_vn, bar_pv};
             chain_roles<NV>(sm, sm_u32, tmem, cb, &tm_q, &tm_k, &tm_w, &tm_p, &tm_u, p, ws, flags, abortp, split, hv, b, bid == 0);
         } else if (!skip_prepare && (warp == 6 || warp >= 8)) {
@@ -689,7 +693,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             else if (lane == 0) publisher_role(r, &tm_w, &tm_us, p, flags, sched, abortp);
         }
     } else if (chain_cta) {
-        if (warp < 6) {
+        if (warp < 4 * (NV / 32) + 2) {
             ChainBars cb{bar_full, bar_empty, &bar_d3, &bar_kv, &bar_vn, bar_pv};
             chain_roles<NV>(sm, sm_u32, tmem, cb, &tm_q, &tm_k, &tm_w, &tm_p, &tm_u, p, ws, flags, abortp, split, hv, b, bid == 0);
         }

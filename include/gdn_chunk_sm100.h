@@ -31,7 +31,8 @@ extern "C" {
 #define GDN_GATE_F32 1
 
 /* execution path */
-#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; COOP when 4*B*Hv <= #SMs; else prepare + chain kernels */
+#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; one launch when 4*B*Hv <= #SMs (COOP_DEDICATED above 1024
+                                    tokens, COOP below); else prepare + chain kernels (64-column chain CTAs)      */
 #define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
 #define GDN_PATH_FUSED_NV64 2    /* single fused tcgen05 kernel, 64 value columns per CTA            */
 #define GDN_PATH_FUSED_NV32 3    /* single fused tcgen05 kernel, 32 value columns per CTA            */
