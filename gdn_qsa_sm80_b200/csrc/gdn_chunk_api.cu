@@ -245,11 +245,12 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     if (path == GDN_PATH_COOP_CHAIN_ONLY)
         return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, true));
     // few independent sequences: one launch holds the chains and the prepare work that feeds them.  Chains on SMs of
-    // their own (64-column CTAs, prepare groups on the other SMs) win once the sequence is long enough to amortise
-    // the prepare lead (measured, 32 sequences x 8192 tokens: 0.231 ms against 0.279 ms; equal within 5 % below 1024
-    // tokens); otherwise a head's four 32-column CTAs share its prepare work among themselves.
+    // their own (64-column CTAs, three prepare groups on each of the other SMs) win once the sequence is long enough
+    // to amortise the prepare lead (measured on one GPU, 8192 tokens: 32 sequences 0.241 ms against 0.260 ms, 36
+    // sequences 0.244 against 0.305; at 2048 tokens 0.082 against 0.080); otherwise a head's four 32-column CTAs
+    // share its prepare work among themselves.
     if (path == GDN_PATH_AUTO && coop_supported(p)) {
-        const bool dedicated = S > 1024 && coop_dedicated_supported(p);
+        const bool dedicated = S > 2048 && coop_dedicated_supported(p);
         return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, false, dedicated));
     }
     if (path == GDN_PATH_COOP)

@@ -31,7 +31,7 @@ extern "C" {
 #define GDN_GATE_F32 1
 
 /* execution path */
-#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; one launch when 4*B*Hv <= #SMs (COOP_DEDICATED above 1024
+#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; one launch when 4*B*Hv <= #SMs (COOP_DEDICATED above 2048
                                     tokens, COOP below); else prepare + chain kernels (64-column chain CTAs)      */
 #define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
 #define GDN_PATH_FUSED_NV64 2    /* single fused tcgen05 kernel, 64 value columns per CTA            */
@@ -43,8 +43,8 @@ extern "C" {
                                     call with the same arguments and scratch left behind              */
 #define GDN_PATH_COOP 8          /* one launch: the four 32-column CTAs of a head share the prepare work
                                     through the workspace while their chains run; needs 4*B*Hv <= #SMs    */
-#define GDN_PATH_COOP_DEDICATED 10 /* one launch: 64-column chain CTAs (2 per head) on SMs of their own, prepare
-                                    groups on all remaining SMs; needs 8*B*Hv <= 3*#SMs                   */
+#define GDN_PATH_COOP_DEDICATED 10 /* one launch: 64-column chain CTAs (2 per head) on SMs of their own, three
+                                    prepare groups on each remaining SM; needs 8*B*Hv <= 3*#SMs           */
 #define GDN_PATH_COOP_CHAIN_ONLY 9 /* measurement aid: COOP with its prepare roles switched off, on the
                                     workspace an earlier call with the same arguments and scratch left  */
 
