@@ -36,7 +36,9 @@ UNIT = "tokens/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one gdn_chain_kernel launch on the default workload (ncu, profiles/)
 CHAIN_DRAM_BYTES_DEFAULT = 361.8e6
-COOP_DRAM_BYTES_DEFAULT = 328.7e6
+# the same for one gdn_coop_kernel launch: dedicated arrangement (path auto on this workload) / in-CTA arrangement
+COOP_DRAM_BYTES_DEFAULT = 451.2e6
+COOP_IN_CTA_DRAM_BYTES_DEFAULT = 328.7e6
 
 
 def flops_per_token(Hq, Hv, C=64, D=128):
@@ -494,7 +496,9 @@ def main():
                     "whole_step": whole}
     elif single_launch:
         # one kernel per step: its duration is the step's (CUDA events around the launch)
-        traffic = COOP_DRAM_BYTES_DEFAULT if (args.workload == "default" and world == 1) else None
+        traffic = None
+        if args.workload == "default" and world == 1:
+            traffic = COOP_IN_CTA_DRAM_BYTES_DEFAULT if args.path == "coop" else COOP_DRAM_BYTES_DEFAULT
         roofline = {"kernel": "gdn_coop_kernel", "bound": "tensor", "achieved": whole["achieved"], "peak": peaks["bf16_tflops"],
                     "unit": "TFLOP/s", "frac": whole["frac"], "traffic": traffic,
                     "peak_kind": f"{peak_kind} (burst cuBLAS bf16)", "algorithmic_flops_per_launch": fl,
