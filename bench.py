@@ -146,13 +146,15 @@ def cpu_arm(workload, seed, min_seconds=10.0, max_reps=12):
     q, k, v, g, beta, h0 = make_inputs(w, seed=seed, B=B, S=S)
     x = [t.float().numpy() for t in (q, k, v, g, beta)]
     h = None if h0 is None else h0.numpy()
-    threads = c_oracle.max_threads()
-    c_oracle.chunk_f32(*x, initial_state=h)   # warm-up (page faults, thread pool)
+    # every host core this process may run on, whatever OMP_NUM_THREADS says: torch.distributed.run sets it to 1 for
+    # its children, which would time a one-thread run as the CPU arm at N > 1
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    c_oracle.chunk_f32(*x, initial_state=h, nthreads=threads)   # warm-up (page faults, thread pool)
     times = []
     t_start = time.perf_counter()
     while len(times) < max_reps and (time.perf_counter() - t_start < min_seconds or len(times) < 3):
         t0 = time.perf_counter()
-        c_oracle.chunk_f32(*x, initial_state=h)
+        c_oracle.chunk_f32(*x, initial_state=h, nthreads=threads)
         times.append(time.perf_counter() - t0)
     tokens = q.shape[0] * q.shape[1]
     med = statistics.median(times)
