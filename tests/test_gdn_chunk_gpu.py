@@ -91,7 +91,13 @@ def test_golden_reference_style_inputs(path):
 def test_cpu_small_workload_on_gpu_matches_stored_reference():
     z = golden("cpu_small.npz")
     q, k, v, g, beta, _ = make_inputs("cpu_small", seed=0)
-    out, st = run(q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16), g, beta)
+    qb, kb, vb = (x.to(torch.bfloat16) for x in (q, k, v))
+    out, st = run(qb, kb, vb, g, beta)
+    # the benchmark's tolerance against the oracle on the values the kernels actually saw (bf16-rounded q, k, v) ...
+    ro, rs = oracle_f32(qb, kb, vb, g, beta)
+    assert_close(out, ro, "out vs oracle")
+    assert_close(st, rs, "state vs oracle")
+    # ... and, loosely, against the reference's stored fp32-input result (the gap is the input rounding)
     assert_close(out[:, ::8], z["out_chunk_every8"], "out", rel=2e-2, mabs=5e-2)
     assert_close(st, z["state_chunk"], "state", rel=2e-2, mabs=5e-2)
 
