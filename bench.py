@@ -14,7 +14,12 @@ events around each step, an L2 flush between steps, max over ranks.  `e2e` is th
 through the public Python API with pinned HOST buffers: host->device copies of all inputs and
 device->host copies of the output and final state inside the timed region.  `cpu_baseline` times
 the CPU oracle (the C restatement of the reference's chunked torch function) on this box's host
-cores.  `--impl reference` prints that CPU arm as its own line.
+cores, and the plain torch definition on the small CPU configuration beside it.
+
+`--impl reference` runs the REFERENCE project's own CUDA kernels (its unmodified sources recompiled
+for sm_100 by `python -m oracle.reference_cuda`, loaded from oracle/_ref/) through its own dispatch
+entry on the same workload, timed the same way, one replica per rank.  When that extension has not
+been built the arm falls back to the CPU port and says so in `reference_kind`.
 """
 
 from __future__ import annotations
@@ -165,6 +170,150 @@ def cpu_arm(workload, seed, min_seconds=10.0, max_reps=12):
             "ms_per_step": med * 1e3}
 
 
+def torch_config0_arm():
+    """The plain torch definition of the operator (fp32, chunk 64) on the small CPU configuration
+    (B1 S512 Hq4 Hv8, zero initial state): 3 warm-ups, median of 10."""
+    import torch
+    from gdn_qsa_sm80_b200.synthetic import make_inputs
+    from gdn_qsa_sm80_b200.torch_definition import chunk_gated_delta_rule
+    q, k, v, g, beta, _ = make_inputs("cpu_small", seed=0)
+    q, k = q.repeat_interleave(2, dim=2), k.repeat_interleave(2, dim=2)
+    times = []
+    for i in range(13):
+        t0 = time.perf_counter()
+        chunk_gated_delta_rule(q, k, v, g, beta, chunk_size=64)
+        if i >= 3:
+            times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return {"value": q.shape[0] * q.shape[1] / med, "unit": UNIT, "ms": med * 1e3, "threads": torch.get_num_threads(),
+            "cores": os.cpu_count(), "sample": "torch fp32 chunked definition, B1 S512 Hq4 Hv8 chunk 64, median of 10"}
+
+
+def reference_arm(args, w, cfg, rank, world, local_rank):
+    """`--impl reference`: the reference project's own kernels on this GPU when its extension was built, else the
+    CPU port.  Same workload, same timing rules, same JSON keys as the main arm."""
+    import torch
+    mod = None
+    why = None
+    if torch.cuda.is_available():
+        try:
+            from oracle import reference_cuda
+            mod = reference_cuda.load()
+            if mod is None:
+                why = "oracle/_ref/_gdn_chunk.so has not been built"
+        except Exception as e:      # the built file does not match this torch / driver
+            why = f"loading the reference's extension failed: {type(e).__name__}: {e}"
+    else:
+        why = "no CUDA device"
+    if mod is None:
+        # CPU arm: the C restatement of the reference's torch function (pinned against it by golden vectors)
+        if rank != 0:
+            return
+        base = cpu_arm(args.workload, args.seed, min_seconds=max(5.0, 0.5 * args.steps))
+        cfg = dict(cfg, sharding=f"{world} independent batch elements, one per GPU, no communication")
+        print(json.dumps({"impl": "reference", "reference_kind": f"cpu port ({why})", "metric": METRIC,
+                          "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+                          "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                          "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}))
+        return
+
+    import torch.distributed as dist
+    from gdn_qsa_sm80_b200.synthetic import make_inputs
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
+        dist.init_process_group("nccl", device_id=dev)
+    # the same share of the workload as the main arm; the reference's entry takes bf16 gates and has no initial state
+    if args.workload == "default" or w.B < world:
+        B_local, total_tokens, scaling = w.B, w.B * w.S * world, "weak"
+        cfg["sharding"] = f"{world} independent batch elements, one per GPU, no communication"
+    else:
+        B_local, total_tokens, scaling = w.B // world, w.B * w.S, "strong"
+        cfg["sharding"] = f"batch split {world} ways ({B_local} per GPU), no communication"
+    q, k, v, g, beta, _ = make_inputs(w, seed=args.seed + rank, B=B_local)
+    host = [t.pin_memory() for t in (q, k, v, g.bfloat16(), beta.bfloat16())]
+    d_in = [t.to(dev, non_blocking=True) for t in host]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step(x=d_in):
+        r = mod.forward_gdn_chunk_auto(x[0], x[1], x[2], x[3], x[4], True)
+        return r[0], r[1]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(args.warmup):
+        step()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        for a, b in ev:
+            flush.zero_()
+            a.record()
+            step()
+            b.record()
+        barrier()
+    ms_per_step = max_over_ranks(sum(a.elapsed_time(b) for a, b in ev)) / args.steps
+    # end to end: pinned host buffers in, results back to pinned host buffers, every step
+    out_host = torch.empty((B_local, w.S, w.Hv, 128), dtype=torch.bfloat16).pin_memory()
+    st_host = torch.empty((B_local, w.Hv, 128, 128), dtype=torch.bfloat16).pin_memory()
+    n_e2e = max(4, min(args.steps, 10))
+
+    def e2e_step():
+        o, s = step([t.to(dev, non_blocking=True) for t in host])
+        out_host.copy_(o, non_blocking=True)
+        st_host.copy_(s, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    b.record()
+    barrier()
+    e2e_ms = max_over_ranks(a.elapsed_time(b)) / n_e2e
+    if rank == 0:
+        peaks, peak_kind = load_peaks()
+        fl = flops_per_token(w.Hq, w.Hv) * B_local * w.S
+        tf = fl / (ms_per_step * 1e-3) / 1e12
+        line = {"impl": "reference",
+                "reference_kind": "the reference's own CUDA kernels (csrc/gdn_chunk, unmodified, recompiled with "
+                                  "-gencode arch=compute_100,code=sm_100) through forward_gdn_chunk_auto; bf16 gates; "
+                                  "zero initial state and bf16 final state (its entry has no others)",
+                "metric": METRIC, "value": total_tokens / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+                "clocks": clocks.summary(),
+                "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT,
+                        "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host),
+                        "d2h_bytes_per_step": out_host.numel() * 2 + st_host.numel() * 2, "steps": n_e2e,
+                        "api": "unpipelined (.to(device) / reference gdn_chunk / .copy_)"},
+                "roofline": {"kernel": "whole step (reference kernels)", "bound": "tensor", "achieved": tf,
+                             "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
+                             "traffic": None, "peak_kind": f"{peak_kind} (burst cuBLAS bf16)"}}
+        if world == 1 and not args.no_cpu_baseline:
+            base = cpu_arm(args.workload, args.seed, min_seconds=max(5.0, 0.5 * args.steps))
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def seq_parallel_arm(args, w, cfg, rank, world, dev):
     """One sequence cut into `world` contiguous segments (multiples of 64 tokens), one per GPU; rank r's segment is
     generated from seed + r (the sequence is the concatenation).  A step = the whole sequence-parallel forward."""
@@ -237,7 +386,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="default", choices=["default", "short_batch", "throughput", "long_context"])
-    ap.add_argument("--path", default="auto", choices=["auto", "simt", "fused_nv64", "fused_nv32", "twopass_nv64", "twopass_nv32", "coop", "coop_dedicated", "decode"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "fused_nv64", "fused_nv32", "twopass_nv64", "twopass_nv32", "twopass_t", "coop", "coop_dedicated", "decode"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -259,19 +408,7 @@ def main():
            "l2": "flushed between timed steps (256 MiB write)", "path": args.path}
 
     if args.impl == "reference":
-        # CPU arm: the reference's own implementation of this path is a torch function that cannot travel
-        # to the GPU box; its C restatement (pinned against it by golden vectors) is timed instead.
-        if rank != 0:
-            return
-        base = cpu_arm(args.workload, args.seed, min_seconds=max(5.0, 0.5 * args.steps))
-        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": cfg,
-                "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
-                "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                "gpu_launches": 0}
-        print(json.dumps(line))
+        reference_arm(args, w, cfg, rank, world, local_rank)
         return
 
     import torch
@@ -443,7 +580,7 @@ def main():
     per_kernel = None
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
     single_launch = args.path == "coop" or (args.path == "auto" and 4 * B_local * w.Hv <= n_sm)
-    cfg["kernels"] = ("gdn_coop_kernel (one launch)" if single_launch else
+    kernels = ("gdn_coop_kernel (one launch)" if single_launch else
                       "gdn_prepare_kernel + gdn_chain_kernel" if args.path in ("auto", "twopass_nv32", "twopass_nv64")
                       else args.path)
     if args.path in ("auto", "twopass_nv32", "twopass_nv64") and not single_launch:
@@ -513,12 +650,13 @@ def main():
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks.summary(),
-            "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline}
+            "e2e": e2e, "gpu_launches": int(launches), "kernels": kernels, "roofline": roofline}
     if with_gate is not None:
         line["with_output_gate"] = with_gate
     if world == 1 and not args.no_cpu_baseline:
         base = cpu_arm(args.workload, args.seed)
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        line["cpu_baseline"]["torch_config0"] = torch_config0_arm()
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -52,13 +52,19 @@ def needs_build() -> bool:
     return (not os.path.exists(LIB_PATH)) or os.path.getmtime(LIB_PATH) < _deps_mtime()
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, diagnostics: bool | None = None) -> str:
+    """diagnostics (default: environment variable GDN_BUILD_DIAGNOSTICS=1) compiles the kernels' cycle accounting in
+    (-DGDN_DIAGNOSTICS); a production build carries none of it."""
+    if diagnostics is None:
+        diagnostics = os.environ.get("GDN_BUILD_DIAGNOSTICS", "0") == "1"
+    if not force and not needs_build() and not diagnostics:
         return LIB_PATH
     nvcc = _nvcc()
     os.makedirs(LIB_DIR, exist_ok=True)
     os.makedirs(OBJ_DIR, exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
+    if diagnostics:
+        extra.append("-DGDN_DIAGNOSTICS")
 
     def compile_one(src):
         obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
@@ -87,5 +93,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register / shared-memory usage")
+    ap.add_argument("--diagnostics", action="store_true", help="compile the kernels' cycle accounting in")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose))
+    print(build(force=a.force, verbose=a.verbose, diagnostics=a.diagnostics or None))

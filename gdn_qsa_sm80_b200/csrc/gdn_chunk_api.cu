@@ -2,6 +2,8 @@
 // encoding through the driver entry point, path selection, status word handling.
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <atomic>
 #include <mutex>
 
@@ -122,14 +124,21 @@ static size_t tiles_of(int B, int S, int Hv) {
 static bool path_uses_workspace(int path) {
     return path == GDN_PATH_AUTO || path == GDN_PATH_TWOPASS_NV64 || path == GDN_PATH_TWOPASS_NV32 ||
            path == GDN_PATH_PREPARE_ONLY || path == GDN_PATH_CHAIN_ONLY || path == GDN_PATH_COOP ||
-           path == GDN_PATH_COOP_CHAIN_ONLY || path == GDN_PATH_COOP_DEDICATED;
+           path == GDN_PATH_COOP_CHAIN_ONLY || path == GDN_PATH_COOP_DEDICATED || path == GDN_PATH_TWOPASS_T;
+}
+
+// segment states the path keeps behind the tile arrays (only the transposed chain splits sequences)
+static size_t seg_states_of(int B, int S, int Hv, int path) {
+    if (path != GDN_PATH_TWOPASS_T && path != GDN_PATH_AUTO) return 0;
+    const int g = chain_segments(B, Hv, S, sm_count());
+    return g > 1 ? static_cast<size_t>(B) * Hv * g : 0;
 }
 
 size_t gdn_chunk_scratch_bytes(int B, int S, int Hq, int Hv, int path) {
     (void)Hq;
     if (B <= 0 || S < 0 || Hv <= 0) return 0;
     if (!path_uses_workspace(path)) return 256;   // only the device status word, padded
-    return workspace_layout(tiles_of(B, S, Hv)).total;
+    return workspace_layout(tiles_of(B, S, Hv), seg_states_of(B, S, Hv, path)).total;
 }
 
 int gdn_chunk_workspace_offsets(int B, int S, int Hq, int Hv, size_t* offsets) {
@@ -178,10 +187,11 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
         return GDN_ERR_BAD_ARGUMENT;
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
-    if (path < GDN_PATH_AUTO || path > GDN_PATH_DECODE) return GDN_ERR_BAD_ARGUMENT;
-    if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u) ||
-        scratch_bytes < gdn_chunk_scratch_bytes(B, S, Hq, Hv, path))
-        return GDN_ERR_SCRATCH;
+    if (path < GDN_PATH_AUTO || path > GDN_PATH_TWOPASS_T) return GDN_ERR_BAD_ARGUMENT;
+    // the least a path needs; gdn_chunk_scratch_bytes may ask for more (room to split long sequences), which is used
+    // when it is there
+    const size_t need = path_uses_workspace(path) ? workspace_layout(tiles_of(B, S, Hv)).total : 256;
+    if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u) || scratch_bytes < need) return GDN_ERR_SCRATCH;
     if (clear_status && cudaMemsetAsync(scratch, 0, 256, stream) != cudaSuccess) return GDN_ERR_CUDA;
     if (S == 0) {   // nothing to scan: the final state is the initial state
         if (hT) {
@@ -211,6 +221,10 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     p.gate_f32 = gate_dtype == GDN_GATE_F32;
     p.l2norm = (flags & GDN_FLAG_QK_L2NORM) ? 1 : 0;
     p.gate_act = (flags & GDN_FLAG_GATE_ACTIVATIONS) ? 1 : 0;
+    {
+        const char* e = getenv("GDN_CHUNK_DBG");
+        p.dbg = e ? atoi(e) : 0;
+    }
     // the normalisation kernel behind whatever produced `out`
     auto then_gate = [&](int st) -> int {
         if (st != GDN_OK || !gate) return st;
@@ -233,13 +247,20 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     else nv = 64;   // more sequences than the single-launch kernel takes: 64-column CTAs need half the waves of
                     // 32-column ones and their chunk step is only ~15 % longer (measured, 4096 tokens: 40 to 64
                     // sequences 0.18-0.22 ms against 0.26-0.30 ms; 96 / 128 sequences 0.37 / 0.42 against 0.43 / 0.57)
-    const WorkspaceLayout l = workspace_layout(tiles_of(B, S, Hv));
+    // the transposed chain splits sequences when the scratch buffer has room for the segment states (a caller that
+    // sized it for an unsplit run, like the fixed-array entry point, gets the unsplit run)
+    size_t seg_states = path == GDN_PATH_TWOPASS_T ? seg_states_of(B, S, Hv, path) : 0;
+    if (seg_states && scratch_bytes < workspace_layout(tiles_of(B, S, Hv), seg_states).total) seg_states = 0;
+    const WorkspaceLayout l = workspace_layout(tiles_of(B, S, Hv), seg_states);
     uint8_t* base = static_cast<uint8_t*>(scratch);
     Workspace ws;
     ws.W = reinterpret_cast<__nv_bfloat16*>(base + l.W);
     ws.P = reinterpret_cast<__nv_bfloat16*>(base + l.P);
     ws.U = reinterpret_cast<__nv_bfloat16*>(base + l.U);
     ws.vec = reinterpret_cast<float*>(base + l.vec);
+    ws.meta = seg_states ? reinterpret_cast<float*>(base + l.meta) : nullptr;
+    ws.seg_state = seg_states ? reinterpret_cast<float*>(base + l.seg_state) : nullptr;
+    ws.n_seg = seg_states ? static_cast<int>(seg_states / (static_cast<size_t>(B) * Hv)) : 1;
     if (path == GDN_PATH_COOP_DEDICATED)
         return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, false, true));
     if (path == GDN_PATH_COOP_CHAIN_ONLY)
@@ -258,6 +279,7 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     if (path == GDN_PATH_CHAIN_ONLY) return then_gate(launch_chain(p, ws, nv, stream));   // workspace left by an earlier call
     const int st = launch_prepare(p, ws, stream);
     if (st != GDN_OK || path == GDN_PATH_PREPARE_ONLY) return st;
+    if (path == GDN_PATH_TWOPASS_T) return then_gate(launch_chain_t(p, ws, stream));
     return then_gate(launch_chain(p, ws, nv, stream));
 }
 }  // namespace gdn
@@ -311,7 +333,7 @@ int gdn_chunk_fwd_sm100_noalloc(const void* q, const void* k, const void* v, con
                                 int gate_dtype, void* stream) {
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     // reject problems whose workspace does not fit the fixed array (the caller gets a clear status, nothing runs)
-    if (gdn_chunk_scratch_bytes(B, S, Hq, Hv, GDN_PATH_AUTO) > kNoAllocBytes) return GDN_ERR_SCRATCH;
+    if (workspace_layout(tiles_of(B, S, Hv)).total > kNoAllocBytes) return GDN_ERR_SCRATCH;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GDN_ERR_CUDA;
     void* addr;

@@ -171,11 +171,17 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             float f[32];
             if (warp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
                 const float bi = p.l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
+                float ksq = 0.f;   // |k_i|^2: the diagonal of K K^T (only for the decay bound of split sequences)
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
                     prep_row_factors(ps, i, half, ri, diag, f);
                     tmem_ld_wait();
+                    if (ws.meta && (i >> 5) == half) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (c == (i & 31)) ksq = __uint_as_float(r[c]);
+                    }
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
                         float4 o;
@@ -185,6 +191,14 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                         o.w = (half * 32 + c + 3 < i) ? bi * f[c + 3] * __uint_as_float(r[c + 3]) : 0.f;
                         *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
                     }
+                }
+                if (ws.meta) {   // max over the chunk of beta_i |k_i|^2, +inf when a gate is outside beta >= 0, g <= 0
+                    const float rk = p.l2norm ? ps.rn[i] : 1.f;
+                    const bool in_range = ps.bet[i] >= 0.f && ps.gam[i] <= (i > 0 ? ps.gam[i - 1] : 0.f);
+                    float bound = in_range ? ps.bet[i] * ksq * rk * rk : INFINITY;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, o));
+                    if ((tid & 31) == 0) ps.wsum[warp] = bound;   // the cumsum's slots are free again by now
                 }
             } else {          // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
                 __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
@@ -207,6 +221,10 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         tc_fence_before_sync();
         __syncthreads();
+        if (ws.meta && tid == 0) {
+            ws.meta[2 * tile] = ps.gam[kChunk - 1] * (1.f / kLog2e);
+            ws.meta[2 * tile + 1] = fmaxf(ps.wsum[0], ps.wsum[1]);
+        }
         GDN_PHASE(3)
 
         prep_invert_unit_lower(As, Tm, Yt);

@@ -28,6 +28,7 @@ struct Problem {
     int gate_f32;          // 0: g/beta are bf16, 1: fp32
     int gate_act;          // 1: g and beta hold raw values; the kernels apply g = -softplus(.), beta = sigmoid(.)
     int l2norm;            // 1: q and k are L2-normalised per head vector inside the kernels
+    int dbg;               // experiment switch (environment variable GDN_CHUNK_DBG); 0 in production
 };
 
 // Workspace of the two-kernel path (device pointers into the caller's scratch buffer).
@@ -37,13 +38,17 @@ struct Workspace {
     __nv_bfloat16* P;   // [tiles][64][64]   masked, scaled Q K^T
     __nv_bfloat16* U;   // [tiles][64][128]  U = T (beta V)
     float* vec;         // [tiles][256]      exp(gamma_C-gamma_i) | scale exp(gamma_i) | exp(gamma_C) | pad
+    float* meta;        // [tiles][2]        sum of g over the chunk | max_j beta_j |k_j|^2 (+inf if a gate is out of range)
+    float* seg_state;   // [B*Hv][n_seg][128][128] fp32: state every segment of a split sequence ends with (may be null)
+    int n_seg;          // segments a sequence is split into by the transposed chain (1 = not split)
 };
 
 // Byte offsets of the workspace arrays inside the scratch buffer (the status word sits at offset 0).
 struct WorkspaceLayout {
-    size_t W, P, U, vec, flags, flag_bytes, total;
+    size_t W, P, U, vec, flags, flag_bytes, meta, seg_state, total;
 };
-inline WorkspaceLayout workspace_layout(size_t tiles) {
+// seg_states: number of 128 x 128 fp32 segment states kept behind the tile arrays (0 when sequences are not split)
+inline WorkspaceLayout workspace_layout(size_t tiles, size_t seg_states = 0) {
     WorkspaceLayout l;
     l.W = 1024;
     l.P = l.W + tiles * 16384;
@@ -51,9 +56,24 @@ inline WorkspaceLayout workspace_layout(size_t tiles) {
     l.vec = l.U + tiles * 16384;
     l.flags = l.vec + tiles * 1024;                      // one int per tile: "prepared" flags of the single-launch path
     l.flag_bytes = (tiles * 4 + 1023) / 1024 * 1024;
-    l.total = l.flags + l.flag_bytes;
+    l.meta = l.flags + l.flag_bytes;
+    l.seg_state = l.meta + (seg_states ? (tiles * 8 + 1023) / 1024 * 1024 : 0);
+    l.total = l.seg_state + seg_states * 65536;
     return l;
 }
+// Into how many contiguous segments the transposed chain splits every sequence (1 = not at all): only when there are
+// too few sequences to fill the GPU, segments of at least 16 chunks, at most 8 of them.  A function of the shape and
+// of the SM count alone.
+inline int chain_segments(int B, int Hv, int S, int sms) {
+    const long long seqs = static_cast<long long>(B) * Hv;
+    const int NT = (S + kChunk - 1) / kChunk;
+    if (seqs * 2 > sms) return 1;
+    int g = static_cast<int>(sms / seqs);
+    if (g > 8) g = 8;
+    if (g > NT / 16) g = NT / 16;
+    return g < 2 ? 1 : g;
+}
+constexpr float kForgetLn = -115.f;   // exp(-115) < 2^-149: a transfer matrix bounded by it is zero in fp32
 
 // Device status codes written by kernels (0 = fine).  The low byte says which wait gave up.
 constexpr int kDevTimeoutTma = 0x101;
@@ -71,6 +91,12 @@ int launch_fused(const Problem& p, int nv, cudaStream_t stream);
 // state recurrence plus outputs, reading the workspace).  Both return a GDN_* status.
 int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream);
 int launch_chain(const Problem& p, const Workspace& ws, int nv, cudaStream_t stream);
+// The chain in transposed form: one CTA per (batch, value head), all 128 value columns (gdn_chain_t_device.cuh).
+// With ws.n_seg > 1 every sequence is cut into ws.n_seg segments that run as independent chains from a zero state,
+// followed by a second launch that recomputes the first chunks of every segment from the state the segment before
+// it ended with - for the heads whose gates make every segment forget its incoming state (decided on the device
+// from ws.meta); the other heads run as one serial chain.  Exact in both cases.
+int launch_chain_t(const Problem& p, const Workspace& ws, cudaStream_t stream);
 // Single-launch variant (prepare shared among the four column CTAs of a head, chain in the same kernel);
 // only when all CTAs fit on the GPU at once.
 bool coop_supported(const Problem& p);

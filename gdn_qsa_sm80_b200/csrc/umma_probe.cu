@@ -80,9 +80,24 @@ umma_probe_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         ok = mbar_wait(&bar_tma, 0, p.status, kDevTimeoutTma);
     } else {
-        for (int e = tid; e < p.M * p.K; e += 128) {
-            const int m = e / p.K, k = e % p.K;
-            *reinterpret_cast<__nv_bfloat16*>(sa + operand_offset(p.a_major, 128, m, k)) = p.a[e];
+        if (p.a_major >= 2) {
+            // A goes to tensor memory: row m on lane m, k pairs packed into 32-bit columns 128 + k/2
+            for (int k0 = 0; k0 < p.K; k0 += 32) {
+                uint32_t r[16];
+                for (int c = 0; c < 16; ++c) {
+                    const __nv_bfloat16 lo = p.a[tid * p.K + k0 + 2 * c], hi = p.a[tid * p.K + k0 + 2 * c + 1];
+                    r[c] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&lo)) |
+                           (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&hi)) << 16);
+                }
+                tmem_st_x16(tmem_addr(tmem, warp * 32, 128 + k0 / 2), r);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+        } else {
+            for (int e = tid; e < p.M * p.K; e += 128) {
+                const int m = e / p.K, k = e % p.K;
+                *reinterpret_cast<__nv_bfloat16*>(sa + operand_offset(p.a_major, 128, m, k)) = p.a[e];
+            }
         }
         for (int e = tid; e < p.N * p.K; e += 128) {
             const int n = e / p.K, k = e % p.K;
@@ -95,16 +110,19 @@ umma_probe_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (ok) {
         if (tid == 0) {
             tc_fence_after_sync();
-            const uint32_t idesc = umma_idesc_bf16(p.M, p.N, p.a_major, p.b_major);
+            const uint32_t idesc = p.a_major >= 2 ? umma_idesc_bf16(p.M, p.N, MAJOR_K, p.b_major, p.a_major == 3)
+                                                  : umma_idesc_bf16(p.M, p.N, p.a_major, p.b_major);
             const uint32_t a0 = smem_u32(sa), b0 = smem_u32(sb);
             for (int ks = 0; ks < p.K / 16; ++ks) {
-                uint64_t ad, bd;
-                if (p.a_major == MAJOR_K) ad = umma_smem_desc(a0 + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, SWZ_128B);
+                uint64_t ad = 0, bd;
+                if (p.a_major >= 2) {}
+                else if (p.a_major == MAJOR_K) ad = umma_smem_desc(a0 + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, SWZ_128B);
                 else ad = umma_smem_desc(a0 + ks * 2048, 16384, 1024, SWZ_128B);
                 if (p.b_major == MAJOR_K) bd = umma_smem_desc(b0 + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, SWZ_128B);
                 else if (p.b_span == 128) bd = umma_smem_desc(b0 + ks * 2048, 16384, 1024, SWZ_128B);
                 else bd = umma_smem_desc(b0 + ks * 1024, 8192, 512, SWZ_64B);
-                umma_bf16_ss(tmem, ad, bd, idesc, ks > 0);
+                if (p.a_major >= 2) umma_bf16_ts(tmem, tmem + 128 + ks * 8, bd, idesc, ks > 0);
+                else umma_bf16_ss(tmem, ad, bd, idesc, ks > 0);
             }
             umma_commit(&bar_mma);
         }
@@ -134,8 +152,9 @@ extern "C" int gdn_umma_probe(const void* a, const void* b, float* d_out, int* s
                               int a_major, int b_major, int b_span, int use_tma, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if ((M != 64 && M != 128) || N < 32 || N > 128 || N % 32 || K < 16 || K > 128 || K % 16) return GDN_ERR_BAD_ARGUMENT;
-    if (a_major < 0 || a_major > 1 || b_major < 0 || b_major > 1 || (b_span != 128 && b_span != 64)) return GDN_ERR_BAD_ARGUMENT;
+    if (a_major < 0 || a_major > 3 || b_major < 0 || b_major > 1 || (b_span != 128 && b_span != 64)) return GDN_ERR_BAD_ARGUMENT;
     if (a_major == MAJOR_MN && M != 128 && M != 64) return GDN_ERR_BAD_ARGUMENT;
+    if (a_major >= 2 && (M != 128 || use_tma || K % 32)) return GDN_ERR_BAD_ARGUMENT;   // A in tensor memory: thread staging only
     if (b_major == MAJOR_MN && b_span == 128 && N % 64) return GDN_ERR_BAD_ARGUMENT;
     if (!a || !b || !d_out || !status_word) return GDN_ERR_BAD_ARGUMENT;
     if (cudaMemsetAsync(status_word, 0, sizeof(int), stream) != cudaSuccess) return GDN_ERR_CUDA;

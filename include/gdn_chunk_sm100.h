@@ -55,6 +55,9 @@ extern "C" {
 #define GDN_PATH_DECODE 11       /* token-by-token fp32 kernel laid out for HBM: one or a few new tokens on top
                                     of a stored state (exact; time grows with S)                         */
 
+#define GDN_PATH_TWOPASS_T 12    /* prepare kernel + transposed chain kernel: one CTA per (batch, value head)
+                                    carries all 128 value columns, state-dependent operands in tensor memory */
+
 #define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
 #define GDN_CHUNK 64             /* tokens per chunk                                                */
 
@@ -223,7 +226,8 @@ void gdn_chunk_set_phase_profile(void* device_buffer);
  *
  *   a_rowmajor [M][K] bf16, b_rowmajor [N][K] bf16 (device) ; d_out [128][N] fp32 (device):
  *   TMEM lanes 0..127 as read back, so an M = 64 product shows where its rows live.
- *   a_major / b_major: 0 = K-major (128-byte swizzled rows), 1 = MN-major;
+ *   a_major / b_major: 0 = K-major (128-byte swizzled rows), 1 = MN-major; a_major 2 = A held in tensor memory
+ *   (K-major, M = 128, thread staging only), 3 = the same with the instruction's negate-A bit set;
  *   b_span: bytes per row of the MN-major B tile (128 or 64); use_tma != 0 stages the tiles
  *   with TMA instead of thread stores.
  * No counterpart in the reference (it unit-tests layouts by hand, csrc/gdn_chunk/gdn_scan_stage1.cu:238-245).

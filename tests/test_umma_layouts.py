@@ -37,6 +37,34 @@ def _mats(M, N, K, seed):
     return a, b
 
 
+# A operand in tensor memory (written by tcgen05.st, one row per lane), as the transposed chain kernel uses it:
+#   S^T W^T / S^T Q^T   (K-major B, 64 tokens, contraction over 128 dk)      v_new^T P^T  (K-major B, contraction over 64)
+#   v~^T K              (MN-major B, 128 dk, contraction over 64 tokens)
+TMEM_A_CASES = [
+    (128, 64, 128, 2, 0, 128),
+    (128, 64, 64, 2, 0, 128),
+    (128, 128, 64, 2, 1, 128),
+    (128, 64, 128, 3, 0, 128),     # negate-A bit
+]
+
+
+@pytest.mark.parametrize("M,N,K,a_major,b_major,b_span", TMEM_A_CASES)
+def test_product_with_a_in_tensor_memory(M, N, K, a_major, b_major, b_span):
+    a, b = _mats(M, N, K, seed=11 + N + K + a_major)
+    d = umma_probe(a.cuda(), b.cuda(), a_major, b_major, b_span, False).cpu()
+    ref = a.float() @ b.float().t()
+    if a_major == 3:
+        ref = -ref
+    assert torch.equal(d[:M], ref), f"max |diff| = {(d[:M] - ref).abs().max().item()}"
+
+
+def test_mn_major_a_with_k_major_b():
+    """U^T I (later V^T T''^T): A = a [tokens][dv] tile read MN-major (M = 128 dv), B K-major."""
+    a, b = _mats(128, 64, 64, seed=3)
+    d = umma_probe(a.cuda(), b.cuda(), 1, 0, 128, False).cpu()
+    assert torch.equal(d[:128], a.float() @ b.float().t())
+
+
 @pytest.mark.parametrize("use_tma", [False, True])
 @pytest.mark.parametrize("M,N,K,a_major,b_major,b_span", CASES)
 def test_product_matches_matmul(M, N, K, a_major, b_major, b_span, use_tma):
