@@ -579,14 +579,17 @@ def main():
     # ---- the two kernels of a step timed on their own (CUDA events on the launching stream, L2 flushed) ----
     per_kernel = None
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
-    single_launch = args.path == "coop" or (args.path == "auto" and 4 * B_local * w.Hv <= n_sm)
+    single_launch = args.path in ("coop", "coop_dedicated") or (args.path == "auto" and w.S <= 2048 and 4 * B_local * w.Hv <= n_sm)
+    transposed = args.path == "twopass_t" or (args.path == "auto" and not single_launch)
     kernels = ("gdn_coop_kernel (one launch)" if single_launch else
-                      "gdn_prepare_kernel + gdn_chain_kernel" if args.path in ("auto", "twopass_nv32", "twopass_nv64")
-                      else args.path)
-    if args.path in ("auto", "twopass_nv32", "twopass_nv64") and not single_launch:
+               "gdn_prepare_kernel + gdn_chain_t_kernel (sequences split on the device: segments, then their first chunks again)"
+               if transposed else
+               "gdn_prepare_kernel + gdn_chain_kernel" if args.path in ("twopass_nv32", "twopass_nv64") else args.path)
+    if transposed or args.path in ("twopass_nv32", "twopass_nv64"):
         per_kernel = {}
         step()                                            # leaves a valid workspace for the chain-only launches
-        for name in ("prepare_only", "chain_only"):
+        for key, name in (("prepare_only", "prepare_only_t" if transposed else "prepare_only"),
+                          ("chain_only", "chain_only_t" if transposed else "chain_only")):
             times = []
             for _ in range(max(3, min(args.steps, 10))):
                 flush.zero_()
@@ -597,7 +600,7 @@ def main():
                 b.record()
                 torch.cuda.synchronize()
                 times.append(a.elapsed_time(b))
-            per_kernel[name] = statistics.median(times)
+            per_kernel[key] = statistics.median(times)
         check_device_status(dev)
 
     if rank != 0:
@@ -623,8 +626,8 @@ def main():
         k_s = per_kernel["chain_only"] * 1e-3
         tf = fl_chain / k_s / 1e12
         # DRAM bytes of one chain launch on the default workload, from an ncu capture (profiles/): read + write
-        traffic = CHAIN_DRAM_BYTES_DEFAULT if (args.workload == "default" and world == 1) else None
-        roofline = {"kernel": "gdn_chain_kernel", "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"],
+        traffic = CHAIN_DRAM_BYTES_DEFAULT if (args.workload == "default" and world == 1 and not transposed) else None
+        roofline = {"kernel": "gdn_chain_t_kernel" if transposed else "gdn_chain_kernel", "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"],
                     "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "traffic": traffic,
                     "peak_kind": f"{peak_kind} (burst cuBLAS bf16)", "algorithmic_flops_per_launch": fl_chain,
                     "kernel_ms": per_kernel["chain_only"],

@@ -38,7 +38,8 @@ FLAG_GATE_ACTIVATIONS = 2
 
 PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "fused_nv64": PATH_FUSED_NV64, "fused_nv32": PATH_FUSED_NV32,
          "twopass_nv64": PATH_TWOPASS_NV64, "twopass_nv32": PATH_TWOPASS_NV32,
-         "prepare_only": PATH_PREPARE_ONLY, "chain_only": PATH_CHAIN_ONLY, "coop": PATH_COOP, "coop_chain_only": PATH_COOP_CHAIN_ONLY, "coop_dedicated": PATH_COOP_DEDICATED, "decode": 11, "twopass_t": 12}
+         "prepare_only": PATH_PREPARE_ONLY, "chain_only": PATH_CHAIN_ONLY, "coop": PATH_COOP, "coop_chain_only": PATH_COOP_CHAIN_ONLY, "coop_dedicated": PATH_COOP_DEDICATED, "decode": 11, "twopass_t": 12,
+         "prepare_only_t": 13, "chain_only_t": 14}
 
 # Every symbol the public header declares (checked by the CPU tests).
 EXPORTS = (

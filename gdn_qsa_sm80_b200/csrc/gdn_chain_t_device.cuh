@@ -5,7 +5,8 @@
 // the state, v_new and its decay-scaled copy) are A operands, which tcgen05.mma may read from tensor memory, and
 // the B operands are tiles exactly as TMA loaded them.  With S^T the [dv x dk] state (thread = one dv row, fp32
 // registers), per 64-token chunk (notation of gdn_qsa_sm80/reference/gdn_chunk_ref.py:90-94):
-//   E0   ACC_VQ  = U^T [I;0]^T          (A = the U tile read MN-major, B = a constant tile: identity over zeros)
+//   E0   ACC_VQ  = V^T [T'';0]^T        (A = the raw V tile read MN-major, B = T'' = T diag(beta) as prepared, over a
+//                                        block of zeros: columns 0-63 become U^T = (T'' V)^T, columns 64-127 zero)
 //   E1   ACC_VQ -= S^T [W;Q]^T          (A = bf16 S^T in TMEM, negated; B = the W and Q tiles as loaded, stacked)
 //        columns 0-63: v_new^T = U^T - S^T W^T (ref :91);  columns 64-127: -(S^T Q^T)
 //   E2   ACC_S  = v~^T K                (A = bf16 v~^T in TMEM, B = K as loaded, MN-major)
@@ -36,12 +37,12 @@ constexpr int kVecSlots = 4;
 constexpr int kThreads = 14 * 32;
 // one stage of the ring (every tile 1024-byte aligned; two 64-column halves of 64 rows x 128 B each)
 // [W;Q]: two dk-halves of 128 rows x 128 B, rows 0-63 W, rows 64-127 Q
-constexpr uint32_t KT = 0, WQ = 16384, UT = 49152, PT = 65536, kStage = 73728;
-constexpr uint32_t kStageTx = kStage + 1024;              // the stage plus its slot of per-token factors
-constexpr uint32_t IDN = kStages * kStage;                // [I;0]: 128 rows x 64 k, bf16, K-major (identity over zeros)
-constexpr uint32_t VEC = IDN + 16384;                     // kVecSlots x 256 floats
+// T2: T'' (64 rows x 128 B) directly followed by ZR, 8 KB of zeros written once: together the 128-row operand [T'';0]
+constexpr uint32_t KT = 0, WQ = 16384, VT = 49152, PT = 65536, T2 = 73728, ZR = 81920, kStage = 90112;
+constexpr uint32_t kStageTx = kStage - 8192 + 1024;       // the stage's tiles (not the zeros) plus its slot of per-token factors
+constexpr uint32_t VEC = kStages * kStage;                // kVecSlots x 256 floats
 constexpr uint32_t kBytes = VEC + kVecSlots * 1024;
-static_assert(kStage % 1024 == 0 && IDN % 1024 == 0, "tiles must stay 1024-byte aligned");
+static_assert(kStage % 1024 == 0 && ZR == T2 + 8192, "tiles must stay 1024-byte aligned; the zeros follow T''");
 
 // tensor-memory columns (32-bit) of one chain CTA
 constexpr uint32_t ACC_S = 0;      // 128: v~^T K
@@ -76,13 +77,12 @@ __device__ __forceinline__ void init_bars(uint64_t* bars) {   // one thread
     mbar_init(&bars[B_PVDONE], 4);
 }
 
-// The constant identity tile (all threads of the CTA; followed by a proxy fence and a CTA barrier in the caller).
-__device__ __forceinline__ void init_identity(uint8_t* sm, int tid, int nthreads) {
-    for (uint32_t e = tid * 16; e < 16384; e += nthreads * 16) *reinterpret_cast<uint4*>(sm + IDN + e) = make_uint4(0, 0, 0, 0);
-}
-__device__ __forceinline__ void init_identity_ones(uint8_t* sm, int tid) {
-    if (tid < 64)
-        *reinterpret_cast<uint16_t*>(sm + IDN + swz_chunk_offset<128>(tid, tid >> 3) + (tid & 7) * 2) = 0x3f80;   // bf16 1.0
+// The blocks of zeros behind every stage's T'' tile (all threads of the CTA; followed by a proxy fence and a CTA
+// barrier in the caller).
+__device__ __forceinline__ void init_zero_blocks(uint8_t* sm, int tid, int nthreads) {
+    for (int s = 0; s < kStages; ++s)
+        for (uint32_t e = tid * 16; e < 8192; e += nthreads * 16)
+            *reinterpret_cast<uint4*>(sm + s * kStage + ZR + e) = make_uint4(0, 0, 0, 0);
 }
 
 __device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
@@ -117,11 +117,12 @@ struct Span {
 };
 
 // `sm`: the CTA's 1024-byte aligned dynamic shared memory (chain region first); `tmem`: base of kTmemCols columns.
-// tm_u: U as 64 x 64 boxes (128-byte swizzle).  flags: per-tile "prepared" flags when WAIT_FLAGS.
+// tm_v: the value tensor (64 x 64 boxes); tm_t2: T'' [tiles * 64][64] (64 x 64 boxes).  flags: per-tile "prepared"
+// flags when WAIT_FLAGS.
 template <bool WAIT_FLAGS>
 __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tmem, const Bars& cb, const CUtensorMap* tm_q,
-                                      const CUtensorMap* tm_k, const CUtensorMap* tm_w, const CUtensorMap* tm_p,
-                                      const CUtensorMap* tm_u, const Problem& p, const Workspace& ws, const int* flags,
+                                      const CUtensorMap* tm_k, const CUtensorMap* tm_v, const CUtensorMap* tm_w,
+                                      const CUtensorMap* tm_p, const CUtensorMap* tm_t2, const Problem& p, const Workspace& ws, const int* flags,
                                       volatile int* abortp, const Span& sp, int hv, int b, bool prof_cta) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hq = hv / (p.Hv / p.Hq);
@@ -155,8 +156,9 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
             mbar_arrive_expect_tx_a(fb, kStageTx);
             tma_load_2d_a(st + WQ, tm_w, fb, 0, row0);
             tma_load_2d_a(st + WQ + 16384, tm_w, fb, 64, row0);
-            tma_load_2d_a(st + UT, tm_u, fb, 0, row0);
-            tma_load_2d_a(st + UT + 8192, tm_u, fb, 64, row0);
+            tma_load_2d_a(st + T2, tm_t2, fb, 0, row0);
+            tma_load_4d_a(st + VT, tm_v, fb, 0, hv, s0, b);
+            tma_load_4d_a(st + VT + 8192, tm_v, fb, 64, hv, s0, b);
             bulk_load_1d_a(sm_u32 + VEC + (n % kVecSlots) * 1024, ws.vec + (tile0 + t) * 256, 1024, fb);
             tma_load_4d_a(st + KT, tm_k, fb, 0, hq, s0, b);
             tma_load_4d_a(st + KT + 8192, tm_k, fb, 64, hq, s0, b);
@@ -173,7 +175,6 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
         constexpr uint32_t idesc_e1 = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_K, 1);    // negated A
         constexpr uint32_t idesc_e2 = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_MN);
         constexpr uint32_t idesc_e3 = umma_idesc_bf16(128, 64, MAJOR_K, MAJOR_K);
-        const uint64_t idn0 = umma_smem_desc(sm_u32 + IDN, 16, 1024, SWZ_128B);
         const bool prof = GDN_DIAG_ON(p.prof != nullptr && prof_cta);
         long long acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long ct = prof ? clock64() : 0;
@@ -193,11 +194,12 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
             tc_fence_after_sync();
             GDN_TPHASE(0)
             GDN_TL(1)
-            {   // E0: ACC_VQ = U^T [I;0]^T
-                const uint64_t a0 = umma_smem_desc(sb + UT, 8192, 1024, SWZ_128B);
+            {   // E0: ACC_VQ = V^T [T'';0]^T
+                const uint64_t a0 = umma_smem_desc(sb + VT, 8192, 1024, SWZ_128B);
+                const uint64_t b0 = umma_smem_desc(sb + T2, 16, 1024, SWZ_128B);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
-                    umma_bf16_ss(tmem + ACC_VQ, a0 + ((ks * 2048) >> 4), idn0 + ((ks * 32) >> 4), idesc_e0, ks > 0);
+                    umma_bf16_ss(tmem + ACC_VQ, a0 + ((ks * 2048) >> 4), b0 + ((ks * 32) >> 4), idesc_e0, ks > 0);
             }
             GDN_TPHASE(1)
             GDN_TL(2)

@@ -124,12 +124,14 @@ static size_t tiles_of(int B, int S, int Hv) {
 static bool path_uses_workspace(int path) {
     return path == GDN_PATH_AUTO || path == GDN_PATH_TWOPASS_NV64 || path == GDN_PATH_TWOPASS_NV32 ||
            path == GDN_PATH_PREPARE_ONLY || path == GDN_PATH_CHAIN_ONLY || path == GDN_PATH_COOP ||
-           path == GDN_PATH_COOP_CHAIN_ONLY || path == GDN_PATH_COOP_DEDICATED || path == GDN_PATH_TWOPASS_T;
+           path == GDN_PATH_COOP_CHAIN_ONLY || path == GDN_PATH_COOP_DEDICATED || path == GDN_PATH_TWOPASS_T ||
+           path == GDN_PATH_PREPARE_ONLY_T || path == GDN_PATH_CHAIN_ONLY_T;
 }
 
 // segment states the path keeps behind the tile arrays (only the transposed chain splits sequences)
 static size_t seg_states_of(int B, int S, int Hv, int path) {
-    if (path != GDN_PATH_TWOPASS_T && path != GDN_PATH_AUTO) return 0;
+    if (path != GDN_PATH_TWOPASS_T && path != GDN_PATH_AUTO && path != GDN_PATH_PREPARE_ONLY_T && path != GDN_PATH_CHAIN_ONLY_T)
+        return 0;
     const int g = chain_segments(B, Hv, S, sm_count());
     return g > 1 ? static_cast<size_t>(B) * Hv * g : 0;
 }
@@ -187,7 +189,7 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
         return GDN_ERR_BAD_ARGUMENT;
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
-    if (path < GDN_PATH_AUTO || path > GDN_PATH_TWOPASS_T) return GDN_ERR_BAD_ARGUMENT;
+    if (path < GDN_PATH_AUTO || path > GDN_PATH_CHAIN_ONLY_T) return GDN_ERR_BAD_ARGUMENT;
     // the least a path needs; gdn_chunk_scratch_bytes may ask for more (room to split long sequences), which is used
     // when it is there
     const size_t need = path_uses_workspace(path) ? workspace_layout(tiles_of(B, S, Hv)).total : 256;
@@ -240,16 +242,22 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     if (path == GDN_PATH_SIMT) return then_gate(launch_simt(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA);
     if (path == GDN_PATH_FUSED_NV64) return then_gate(launch_fused(p, 64, stream));
     if (path == GDN_PATH_FUSED_NV32) return then_gate(launch_fused(p, 32, stream));
-    // two-kernel path: "prepare" over all chunks in parallel, then the serial "chain"
+    // Automatic choice, by shape alone.  Few short sequences: the single-launch kernel whose four 32-column CTAs per
+    // head share the prepare work (2048 tokens, 32 sequences: 0.080 ms).  Everything else: the prepare kernel and the
+    // transposed chain (one CTA per head, state-dependent operands in tensor memory), which splits long sequences
+    // into segments when there are too few of them to fill the GPU.  Measured on one B200 against the earlier
+    // arrangements (64-column chain CTAs; single launch with dedicated chain SMs): 8192 tokens x 32 sequences 0.197 ms
+    // against 0.241; 512 sequences x 2048 tokens 0.63 against 0.75; 2048 x 4096 4.6 against 5.6; one 131072-token
+    // sequence x 32 heads 2.5 against 3.9.
+    const bool automatic = path == GDN_PATH_AUTO;
+    if (automatic) path = (S <= 2048 && coop_supported(p)) ? GDN_PATH_COOP : GDN_PATH_TWOPASS_T;
     int nv;
-    if (path == GDN_PATH_TWOPASS_NV64) nv = 64;
-    else if (path == GDN_PATH_TWOPASS_NV32) nv = 32;
-    else nv = 64;   // more sequences than the single-launch kernel takes: 64-column CTAs need half the waves of
-                    // 32-column ones and their chunk step is only ~15 % longer (measured, 4096 tokens: 40 to 64
-                    // sequences 0.18-0.22 ms against 0.26-0.30 ms; 96 / 128 sequences 0.37 / 0.42 against 0.43 / 0.57)
+    if (path == GDN_PATH_TWOPASS_NV32) nv = 32;
+    else nv = 64;
     // the transposed chain splits sequences when the scratch buffer has room for the segment states (a caller that
     // sized it for an unsplit run, like the fixed-array entry point, gets the unsplit run)
-    size_t seg_states = path == GDN_PATH_TWOPASS_T ? seg_states_of(B, S, Hv, path) : 0;
+    const bool transposed = path == GDN_PATH_TWOPASS_T || path == GDN_PATH_PREPARE_ONLY_T || path == GDN_PATH_CHAIN_ONLY_T;
+    size_t seg_states = transposed ? seg_states_of(B, S, Hv, path) : 0;
     if (seg_states && scratch_bytes < workspace_layout(tiles_of(B, S, Hv), seg_states).total) seg_states = 0;
     const WorkspaceLayout l = workspace_layout(tiles_of(B, S, Hv), seg_states);
     uint8_t* base = static_cast<uint8_t*>(scratch);
@@ -265,20 +273,19 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
         return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, false, true));
     if (path == GDN_PATH_COOP_CHAIN_ONLY)
         return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, true));
-    // few independent sequences: one launch holds the chains and the prepare work that feeds them.  Chains on SMs of
-    // their own (64-column CTAs, three prepare groups on each of the other SMs) win once the sequence is long enough
-    // to amortise the prepare lead (measured on one GPU, 8192 tokens: 32 sequences 0.241 ms against 0.260 ms, 36
-    // sequences 0.244 against 0.305; at 2048 tokens 0.082 against 0.080); otherwise a head's four 32-column CTAs
-    // share its prepare work among themselves.
-    if (path == GDN_PATH_AUTO && coop_supported(p)) {
-        const bool dedicated = S > 2048 && coop_dedicated_supported(p);
-        return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, false, dedicated));
+    if (path == GDN_PATH_COOP) {
+        const int st = launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream);
+        // the single-launch kernel is a cooperative launch: when its grid cannot be resident all at once on this
+        // context (fewer SMs than the device reports, a limited partition) the launch is refused and nothing has
+        // run; the automatic path then takes the two-kernel route, which waits for nothing inside a launch
+        if (!(automatic && st == GDN_ERR_CUDA)) return then_gate(st);
+        (void)cudaGetLastError();
+        path = GDN_PATH_TWOPASS_T;
     }
-    if (path == GDN_PATH_COOP)
-        return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream));
     if (path == GDN_PATH_CHAIN_ONLY) return then_gate(launch_chain(p, ws, nv, stream));   // workspace left by an earlier call
-    const int st = launch_prepare(p, ws, stream);
-    if (st != GDN_OK || path == GDN_PATH_PREPARE_ONLY) return st;
+    if (path == GDN_PATH_CHAIN_ONLY_T) return then_gate(launch_chain_t(p, ws, stream));
+    const int st = launch_prepare(p, ws, stream, !transposed);
+    if (st != GDN_OK || path == GDN_PATH_PREPARE_ONLY || path == GDN_PATH_PREPARE_ONLY_T) return st;
     if (path == GDN_PATH_TWOPASS_T) return then_gate(launch_chain_t(p, ws, stream));
     return then_gate(launch_chain(p, ws, nv, stream));
 }

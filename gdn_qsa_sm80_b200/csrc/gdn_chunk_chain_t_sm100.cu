@@ -64,8 +64,9 @@ __device__ __forceinline__ bool head_is_splittable(const float* meta, int NT, in
 template <int PASS>
 __global__ void __launch_bounds__(chain_t::kThreads, 1)
 gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_p,
-                   const __grid_constant__ CUtensorMap tm_u, Problem p, Workspace ws, int L) {
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
+                   const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_t2, Problem p,
+                   Workspace ws, int L) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sm_u32 = smem_u32(sm);
@@ -95,9 +96,7 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const bool ok = head_is_splittable(ws.meta + seq * NT * 2, NT, ws.n_seg, L, lane, horizon);
         if (lane == 0) split_ok = ok ? 1 : 0;
     }
-    chain_t::init_identity(sm, tid, chain_t::kThreads);
-    __syncthreads();
-    chain_t::init_identity_ones(sm, tid);
+    chain_t::init_zero_blocks(sm, tid, chain_t::kThreads);
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -126,7 +125,7 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
     }
     if (sp.t0 < sp.t1)
-        chain_t::roles<false>(sm, sm_u32, tmem, cb, &tm_q, &tm_k, &tm_w, &tm_p, &tm_u, p, ws, nullptr, abortp, sp, hv, b,
+        chain_t::roles<false>(sm, sm_u32, tmem, cb, &tm_q, &tm_k, &tm_v, &tm_w, &tm_p, &tm_t2, p, ws, nullptr, abortp, sp, hv, b,
                               blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
 
     tc_fence_before_sync();
@@ -142,14 +141,20 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 }  // namespace
 
 int launch_chain_t(const Problem& p, const Workspace& ws, cudaStream_t stream) {
-    alignas(64) CUtensorMap tq, tk, tv, tw, tp, tus;
+    alignas(64) CUtensorMap tq, tk, tv, tw, tp, tt2;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
-    if (encode_workspace_maps(p, ws, &tw, &tp, &tus, nullptr, 64)) return GDN_ERR_DRIVER;
+    if (encode_workspace_maps(p, ws, &tw, &tp, nullptr, nullptr, 64)) return GDN_ERR_DRIVER;
+    {   // T'' = T diag(beta): [tiles * 64][64] bf16 at the start of the U array
+        const unsigned long long rows = static_cast<unsigned long long>(p.B) * p.Hv * ((p.S + kChunk - 1) / kChunk) * kChunk;
+        const unsigned long long d[2] = {64, rows}, sb[1] = {128};
+        const unsigned box[2] = {64, 64};
+        if (encode_tma(&tt2, ws.U, 2, 2, d, sb, box, 128)) return GDN_ERR_DRIVER;
+    }
     const uint32_t smem = chain_t::kBytes + 1024;
     const int NT = (p.S + kChunk - 1) / kChunk;
     auto go = [&](auto kernel, unsigned gz, int L) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return GDN_ERR_CUDA;
-        kernel<<<dim3(p.Hv, p.B, gz), chain_t::kThreads, smem, stream>>>(tq, tk, tw, tp, tus, p, ws, L);
+        kernel<<<dim3(p.Hv, p.B, gz), chain_t::kThreads, smem, stream>>>(tq, tk, tv, tw, tp, tt2, p, ws, L);
         count_launch();
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };

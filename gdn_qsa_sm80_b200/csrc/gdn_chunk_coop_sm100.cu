@@ -21,9 +21,10 @@
 //                      its publisher) and walk the tiles chunk-major (every head's chunk 0, then chunk 1, ...), so
 //                      the chain shares its SM with nobody.  Needs 2*B*Hv plus a few CTAs <= #SMs.
 //
-// All CTAs must be resident together (one CTA per SM because of its shared memory; the host checks the grid
-// against the number of SMs).  Waiting is on flags written inside the same launch; every wait is bounded and a
-// wait that runs out sets the status word and drains the CTA.
+// All CTAs must be resident together (one CTA per SM because of its shared memory): the kernel is launched
+// cooperatively, so the runtime refuses a grid that cannot be resident at once and schedules it as a whole.
+// Waiting is on flags written inside the same launch; every wait is bounded and a wait that runs out sets the
+// status word and drains the CTA.
 #include <cuda.h>
 
 #include "../../include/gdn_chunk_sm100.h"
@@ -994,9 +995,26 @@ int launch_coop_t(const Problem& p, const Workspace& ws, int* flags, size_t flag
                                      : L::kChainBytes + kPrepBytes) + 1024;
     auto go = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return GDN_ERR_CUDA;
-        kernel<<<grid, 384, smem, stream>>>(tq, tk, tv, tw, tp, tu, tus, p, ws, flags, skip_prepare ? 1 : 0, n_chain);
+        // Cooperative launch: the CTAs wait on flags raised by other CTAs of the same grid, so all of them must be
+        // resident together.  The runtime checks that against the occupancy of this context and refuses the launch
+        // (nothing runs) when the grid does not fit, instead of letting part of it spin until the wait limit.
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(384);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tq, tk, tv, tw, tp, tu, tus, p, ws, flags, skip_prepare ? 1 : 0, n_chain);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return GDN_ERR_CUDA;
+        }
         count_launch();
-        return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
+        return GDN_OK;
     };
     return p.gate_f32 ? go(gdn_coop_kernel<NV, DEDICATED, true>) : go(gdn_coop_kernel<NV, DEDICATED, false>);
 }

@@ -42,7 +42,9 @@ struct PSmem {
 constexpr uint32_t kPrepTmemCols = 128;
 constexpr int kPrepCtasPerSm = 3;
 
-template <bool GATE_F32>
+// WITH_U = false: for the transposed chain, which forms U^T = V^T T''^T itself from the raw V tile: no V load, no
+// second product, no U tile; T'' = T diag(beta) (bf16, 64 x 64, row-major) goes to the workspace instead.
+template <bool GATE_F32, bool WITH_U>
 __global__ void __launch_bounds__(128, kPrepCtasPerSm)
 gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
@@ -154,7 +156,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // TMA wait and the first UMMAs have hidden most of that latency.  Q is dead now: V takes its place.
         if (tid == 0) {
             tma_store_wait_read();
-            issue_v(cur);
+            if (WITH_U) issue_v(cur);
         }
         ok = __syncthreads_and(ok);
         if (!ok) break;
@@ -232,14 +234,19 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
         {   // [T diag(beta e^gamma) ; T diag(beta)] as one 128-row K-major operand
             const int which = tid >> 6;
-            prep_store_scaled_T_row(Tm, which == 0 ? ps.eg : ps.bet, i, sm + PSmem::AS, which * 64 + i);   // A is dead
+            if (WITH_U || which == 0)
+                prep_store_scaled_T_row(Tm, which == 0 ? ps.eg : ps.bet, i, sm + PSmem::AS, which * 64 + i);   // A is dead
+            else   // T'' leaves as it is (operand rows 64-127 stay undefined: their product rows are never read)
+                prep_store_scaled_T_row_plain(Tm, ps.bet, i, ws.U + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
         }
         fence_proxy_async_smem();
         __syncthreads();
-        ok = mbar_wait(&bar_tma, ph_tma, p.status, kDevTimeoutTma);   // V has landed
-        ph_tma ^= 1;
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
+        if (WITH_U) {
+            ok = mbar_wait(&bar_tma, ph_tma, p.status, kDevTimeoutTma);   // V has landed
+            ph_tma ^= 1;
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+        }
         GDN_PHASE(5)
 
         // W = T' K and U = T'' V go through the same 128 TMEM columns one after the other.  Both products use the
@@ -278,6 +285,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 }
             }
         }
+        if (WITH_U) {
         tc_fence_before_sync();
         __syncthreads();          // W has left the accumulator
         if (tid == 0) {
@@ -294,6 +302,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ph_mma ^= 1;
         ok = __syncthreads_and(ok);
         if (!ok) break;
+        }
         GDN_PHASE(6)
 
         // K, V and the [T';T''] operand are dead: start the next tile's loads and gate reads before the epilogue
@@ -306,7 +315,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                                       min(kChunk, p.S - nxt.s0), gv, bv, PrepCtx::whole_cta(), p.gate_act != 0);
         }
         tc_fence_after_sync();
-        if (warp >= 2) {   // U rows (lanes 64-127) -> staging tile in the A buffer (the operand there is dead)
+        if (WITH_U && warp >= 2) {   // U rows (lanes 64-127) -> staging tile in the A buffer (the operand there is dead)
             uint32_t r[32];
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
@@ -331,8 +340,10 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             const int row0 = static_cast<int>(tile * kChunk);
             tma_store_2d(&tm_w, sm + PSmem::TM, 0, row0);
             tma_store_2d(&tm_w, sm + PSmem::TM + 8192, 64, row0);
+            if (WITH_U) {
 #pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) tma_store_2d(&tm_u, sm + PSmem::AS + h2 * 8192, h2 * 64, row0);
+                for (int h2 = 0; h2 < 2; ++h2) tma_store_2d(&tm_u, sm + PSmem::AS + h2 * 8192, h2 * 64, row0);
+            }
             tma_store_commit();
         }
         GDN_PHASE(7)
@@ -352,7 +363,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
 }  // namespace
 
-int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream) {
+int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream, bool with_u) {
     alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
     if (encode_workspace_maps(p, ws, &tw, &tp, &tu, nullptr, 64)) return GDN_ERR_DRIVER;
@@ -367,7 +378,8 @@ int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream) {
         count_launch();
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };
-    return p.gate_f32 ? go(gdn_prepare_kernel<true>) : go(gdn_prepare_kernel<false>);
+    if (with_u) return p.gate_f32 ? go(gdn_prepare_kernel<true, true>) : go(gdn_prepare_kernel<false, true>);
+    return p.gate_f32 ? go(gdn_prepare_kernel<true, false>) : go(gdn_prepare_kernel<false, false>);
 }
 
 }  // namespace gdn

@@ -36,7 +36,7 @@ struct Problem {
 struct Workspace {
     __nv_bfloat16* W;   // [tiles][64][128]  W = T (beta e^gamma K)
     __nv_bfloat16* P;   // [tiles][64][64]   masked, scaled Q K^T
-    __nv_bfloat16* U;   // [tiles][64][128]  U = T (beta V)
+    __nv_bfloat16* U;   // [tiles][64][128]  U = T (beta V); the transposed chain's T'' = T diag(beta), [tiles][64][64], instead
     float* vec;         // [tiles][256]      exp(gamma_C-gamma_i) | scale exp(gamma_i) | exp(gamma_C) | pad
     float* meta;        // [tiles][2]        sum of g over the chunk | max_j beta_j |k_j|^2 (+inf if a gate is out of range)
     float* seg_state;   // [B*Hv][n_seg][128][128] fp32: state every segment of a split sequence ends with (may be null)
@@ -89,7 +89,9 @@ int launch_fused(const Problem& p, int nv, cudaStream_t stream);
 
 // "prepare" (state-independent per-chunk quantities into the workspace) and "chain" (the serial
 // state recurrence plus outputs, reading the workspace).  Both return a GDN_* status.
-int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream);
+// with_u = false (for the transposed chain): no U tile; T'' = T diag(beta), bf16 [tiles][64][64], is written at the
+// start of the U array instead.
+int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream, bool with_u = true);
 int launch_chain(const Problem& p, const Workspace& ws, int nv, cudaStream_t stream);
 // The chain in transposed form: one CTA per (batch, value head), all 128 value columns (gdn_chain_t_device.cuh).
 // With ws.n_seg > 1 every sequence is cut into ws.n_seg segments that run as independent chains from a zero state,

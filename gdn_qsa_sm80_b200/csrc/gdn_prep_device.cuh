@@ -361,4 +361,21 @@ __device__ __forceinline__ void prep_store_scaled_T_row(const float* Tm, const f
     }
 }
 
+// Row `i` of  T diag(f)  as bf16 into a plain row-major row of 64 values in global memory (16-byte stores).
+__device__ __forceinline__ void prep_store_scaled_T_row_plain(const float* Tm, const float* f, int i, __nv_bfloat16* dst) {
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+        const float4 t0 = *reinterpret_cast<const float4*>(Tm + i * kSolveStride + ch * 8);
+        const float4 t1 = *reinterpret_cast<const float4*>(Tm + i * kSolveStride + ch * 8 + 4);
+        const float4 f0 = *reinterpret_cast<const float4*>(f + ch * 8);
+        const float4 f1 = *reinterpret_cast<const float4*>(f + ch * 8 + 4);
+        uint4 pk;
+        pk.x = pack_bf16x2(t0.x * f0.x, t0.y * f0.y);
+        pk.y = pack_bf16x2(t0.z * f0.z, t0.w * f0.w);
+        pk.z = pack_bf16x2(t1.x * f1.x, t1.y * f1.y);
+        pk.w = pack_bf16x2(t1.z * f1.z, t1.w * f1.w);
+        *reinterpret_cast<uint4*>(dst + ch * 8) = pk;
+    }
+}
+
 }  // namespace gdn

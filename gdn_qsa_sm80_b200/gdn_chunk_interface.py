@@ -149,21 +149,22 @@ def _forward(q, k, v, g, beta, output_final_state, initial_state, path, l2norm=F
 
 
 def check_device_status(device=None):
-    """Synchronise the current stream of `device` and raise if the last kernel launched on it reported a bounded wait
-    that ran out."""
+    """Synchronise every stream of `device` this module has launched on and raise if a kernel on any of them
+    reported a bounded wait that ran out (its result is then undefined).  Callers that launch asynchronously and
+    never come here should call this before they trust a result; the module's own synchronising calls do."""
     import ctypes
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
-    buf = _scratch.get((device.index, torch.cuda.current_stream(device).cuda_stream))
-    if buf is None:
-        return
-    word = ctypes.c_int(0)
-    with torch.cuda.device(device):
-        st = _lib.load().gdn_chunk_read_status(buf.data_ptr(), torch.cuda.current_stream(device).cuda_stream,
-                                               ctypes.byref(word))
-    if st != _lib.GDN_OK:
-        raise _lib.GdnLibraryError(f"device status 0x{word.value:x}: {_lib.error_string(st)}")
+    lib = _lib.load()
+    for (index, stream), buf in list(_scratch.items()):
+        if index != device.index:
+            continue
+        word = ctypes.c_int(0)
+        with torch.cuda.device(device):
+            st = lib.gdn_chunk_read_status(buf.data_ptr(), stream, ctypes.byref(word))
+        if st != _lib.GDN_OK:
+            raise _lib.GdnLibraryError(f"device status 0x{word.value:x}: {_lib.error_string(st)}")
 
 
 def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, path="auto",

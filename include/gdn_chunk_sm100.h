@@ -31,8 +31,7 @@ extern "C" {
 #define GDN_GATE_F32 1
 
 /* execution path */
-#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; one launch when 4*B*Hv <= #SMs (COOP_DEDICATED above 2048
-                                    tokens, COOP below); else prepare + chain kernels (64-column chain CTAs)      */
+#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; COOP when S <= 2048 and 4*B*Hv <= #SMs; else TWOPASS_T     */
 #define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
 #define GDN_PATH_FUSED_NV64 2    /* single fused tcgen05 kernel, 64 value columns per CTA            */
 #define GDN_PATH_FUSED_NV32 3    /* single fused tcgen05 kernel, 32 value columns per CTA            */
@@ -57,6 +56,10 @@ extern "C" {
 
 #define GDN_PATH_TWOPASS_T 12    /* prepare kernel + transposed chain kernel: one CTA per (batch, value head)
                                     carries all 128 value columns, state-dependent operands in tensor memory */
+
+#define GDN_PATH_PREPARE_ONLY_T 13 /* measurement aid: only the prepare kernel as TWOPASS_T runs it          */
+#define GDN_PATH_CHAIN_ONLY_T 14   /* measurement aid: only the transposed chain, on the workspace an earlier
+                                      TWOPASS_T / PREPARE_ONLY_T call with the same arguments and scratch left */
 
 #define GDN_D 128                /* head dimension of keys and values (compile-time in the kernels) */
 #define GDN_CHUNK 64             /* tokens per chunk                                                */

@@ -127,7 +127,7 @@ def test_long_context_workload_full_size():
 
 
 def test_throughput_workload_full_size():
-    """B64 S4096 (2048 independent sequences, two-kernel path): against the fp32 recurrent kernel on the whole batch,
+    """B64 S4096 (2048 independent sequences, prepare + transposed chain): against the fp32 recurrent kernel on the whole batch,
     and batch independence: a batch slice run alone gives the same bits as its part of the full run."""
     w, q, k, v, g, beta, h0 = _device_inputs("throughput", 4)
     out, st = gdn_chunk(q, k, v, g, beta, initial_state=h0)
@@ -137,5 +137,5 @@ def test_throughput_workload_full_size():
     assert float((out.float() - o2.float()).abs().max()) <= 2e-2
     del o2, s2
     sl = slice(40, 44)
-    o3, s3 = gdn_chunk(q[sl], k[sl], v[sl], g[sl], beta[sl], initial_state=h0[sl], path="twopass_nv64")
+    o3, s3 = gdn_chunk(q[sl], k[sl], v[sl], g[sl], beta[sl], initial_state=h0[sl], path="twopass_t")
     assert torch.equal(o3, out[sl]) and torch.equal(s3, st[sl])
