@@ -314,6 +314,144 @@ def reference_arm(args, w, cfg, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def device_inputs(w, seed, dev, B=None, S=None):
+    """A workload's distributions drawn on the GPU generator (the CPU generator takes minutes at the large sizes)."""
+    import torch
+    F = torch.nn.functional
+    B = w.B if B is None else B
+    S = w.S if S is None else S
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=gen, device=dev)
+    q = F.normalize(rn(B, S, w.Hq, 128), dim=-1).bfloat16()
+    k = F.normalize(rn(B, S, w.Hq, 128), dim=-1).bfloat16()
+    v = rn(B, S, w.Hv, 128).bfloat16()
+    g = -F.softplus(rn(B, S, w.Hv)) * w.gate_scale
+    beta = torch.sigmoid(rn(B, S, w.Hv))
+    h0 = 0.1 * rn(B, w.Hv, 128, 128) if w.h0 != "zeros" else None
+    return q, k, v, g, beta, h0
+
+
+def timed_steps(step, steps, warmup, flush, dev, world, barrier_each=False):
+    """ms per step: CUDA events around every step on the current stream, an L2 flush before each, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(warmup):
+        flush.zero_()
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    total = 0.0
+    for _ in range(steps):
+        flush.zero_()
+        if barrier_each and world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total += float(t.item())
+    return total / steps
+
+
+def sharded_arm(rank, world, dev, flush, seed, steps=5, warmup=3):
+    """The throughput workload (B=64 S=4096) split over the ranks by batch, no communication: strong scaling."""
+    import torch
+    from gdn_qsa_sm80 import gdn_chunk
+    from gdn_qsa_sm80_b200.synthetic import WORKLOADS
+    w = WORKLOADS["throughput"]
+    if w.B % world:
+        return None
+    Bl = w.B // world
+    q, k, v, g, beta, h0 = device_inputs(w, seed + 100 + rank, dev, B=Bl)
+    ms = timed_steps(lambda: gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=h0), steps, warmup,
+                     flush, dev, world)
+    del q, k, v, g, beta, h0
+    torch.cuda.empty_cache()
+    tokens = w.B * w.S
+    return {"workload": f"throughput: B={w.B} S={w.S} Hq={w.Hq} Hv={w.Hv} h0={w.h0}, batch split {world} ways "
+                        f"({Bl} per GPU), no communication", "scaling": "strong", "value": tokens / (ms * 1e-3),
+            "unit": UNIT, "ms_per_step": ms, "steps": steps, "warmup": warmup,
+            "frac_of_bf16_peak": tokens * flops_per_token(w.Hq, w.Hv) / (ms * 1e-3) / 1e12 / (load_peaks()[0]["bf16_tflops"] * world)}
+
+
+def seq_parallel_measure(rank, world, dev, flush, seed, steps=5, warmup=3):
+    """The long_context workload (one sequence of 131072 tokens) cut into `world` contiguous segments, boundary
+    states exchanged by NCCL send/recv (scan mode with the exact early-out)."""
+    import torch
+    from gdn_qsa_sm80_b200.distributed import segment_bounds, sequence_parallel_forward
+    from gdn_qsa_sm80_b200.synthetic import WORKLOADS
+    w = WORKLOADS["long_context"]
+    lo, hi = segment_bounds(w.S, world)[rank]
+    q, k, v, g, beta, _ = device_inputs(w, seed + 200 + rank, dev, S=hi - lo)
+    ms = timed_steps(lambda: sequence_parallel_forward(q, k, v, g, beta, initial_state=None, mode="scan"), steps,
+                     warmup, flush, dev, world, barrier_each=True)
+    del q, k, v, g, beta
+    torch.cuda.empty_cache()
+    tokens = w.B * w.S
+    return {"workload": f"long_context: B=1 S={w.S} Hq={w.Hq} Hv={w.Hv}, one sequence in {world} contiguous segments, "
+                        f"boundary states [Hv,128,128] fp32 by NCCL send/recv, scan mode", "scaling": "strong",
+            "value": tokens / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "steps": steps, "warmup": warmup}
+
+
+def link_ceiling(host_in, host_out, dev, world, reps=4):
+    """Plain cudaMemcpyAsync of one step's bytes, host->device and device->host at the same time on two streams, on
+    every rank at once: what the host link gives with no kernel in the way.  Returns GB/s per direction (this rank,
+    min over ranks reported by the caller) and the step time."""
+    import torch
+    import torch.distributed as dist
+    d_in = [torch.empty_like(t, device=dev) for t in host_in]
+    d_out = [torch.empty_like(t, device=dev) for t in host_out]
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def once():
+        with torch.cuda.stream(s1):
+            for h, d in zip(host_in, d_in):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(s2):
+            for h, d in zip(host_out, d_out):
+                h.copy_(d, non_blocking=True)
+
+    once()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        once()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / reps
+    t = torch.tensor([dt], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def bind_near_gpu(index):
+    """Run this process's threads on the CPUs NVML lists as local to the GPU (read-only query; changes only this
+    process's own affinity).  Returns a short description for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        n = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, n)
+        cpus = {64 * i + b for i, word in enumerate(mask) for b in range(64) if (word >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        use = cpus & allowed
+        if use and use != allowed:
+            os.sched_setaffinity(0, use)
+            return f"threads bound to the {len(use)} CPUs local to GPU {index}"
+        return f"GPU {index}: every allowed CPU ({len(allowed)}) is local (one NUMA node visible)"
+    except Exception as e:       # no NVML / no permission: leave the affinity alone
+        return f"affinity unchanged ({type(e).__name__})"
+
+
 def seq_parallel_arm(args, w, cfg, rank, world, dev):
     """One sequence cut into `world` contiguous segments (multiples of 64 tokens), one per GPU; rank r's segment is
     generated from seed + r (the sequence is the concatenation).  A step = the whole sequence-parallel forward."""
@@ -390,6 +528,8 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-multi", action="store_true",
+                    help="skip the extra keys \"sharded\" (throughput workload split over the GPUs) and \"seq_parallel\"")
     ap.add_argument("--seq-parallel", default=None, choices=["pipeline", "scan", "scan_no_early_out"],
                     help="with --gpus N > 1: split ONE sequence of the workload into N contiguous segments, one per "
                          "GPU, boundary states exchanged by send/recv (strong scaling)")
@@ -422,6 +562,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU path for the operator")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    affinity = bind_near_gpu(local_rank)                 # before the pinned host buffers are allocated
     if world > 1:
         os.environ.setdefault("NCCL_DEBUG", "WARN")      # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
@@ -544,8 +685,16 @@ def main():
             modes["gdn_chunk_host, one call at a time"] = time_e2e(e2e_piped)
             modes["gdn_chunk_host, two calls in flight"] = time_e2e(e2e_piped2)
         best = max(modes, key=modes.get)
+        step_s = total_tokens / modes[best] / world          # seconds per step and rank at the best mode
+        ceil_s = link_ceiling([t for t in host if t is not None], [out_host, st_host], dev, world)
         e2e = {"value": modes[best], "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "steps": n_e2e, "api": best, "all": modes}
+               "steps": n_e2e, "api": best, "all": modes,
+               "achieved_h2d_gbs_per_gpu": h2d / step_s / 1e9, "achieved_d2h_gbs_per_gpu": d2h / step_s / 1e9,
+               "link_ceiling": {"what": "the same bytes by plain cudaMemcpyAsync, both directions at once, all ranks at once, "
+                                        "no kernel (slowest rank)", "ms_per_step": ceil_s * 1e3,
+                                "value": total_tokens / ceil_s, "unit": UNIT,
+                                "h2d_gbs_per_gpu": h2d / ceil_s / 1e9, "d2h_gbs_per_gpu": d2h / ceil_s / 1e9},
+               "host_affinity": affinity}
 
     # ---- optional: the layer's next step (gated RMS normalisation of O) chained behind the forward pass ----
     with_gate = None
@@ -603,6 +752,15 @@ def main():
             per_kernel[key] = statistics.median(times)
         check_device_status(dev)
 
+    # ---- the two multi-GPU cases of the specification, on the plain line (default workload only) ----------
+    sharded = seq_par = None
+    if args.workload == "default" and args.path == "auto" and not args.no_multi:
+        del d_in
+        torch.cuda.empty_cache()
+        sharded = sharded_arm(rank, world, dev, flush, args.seed)
+        if world > 1:
+            seq_par = seq_parallel_measure(rank, world, dev, flush, args.seed)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -654,6 +812,10 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks.summary(),
             "e2e": e2e, "gpu_launches": int(launches), "kernels": kernels, "roofline": roofline}
+    if sharded is not None:
+        line["sharded"] = sharded
+    if seq_par is not None:
+        line["seq_parallel"] = seq_par
     if with_gate is not None:
         line["with_output_gate"] = with_gate
     if world == 1 and not args.no_cpu_baseline:

@@ -284,7 +284,8 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     }
     if (path == GDN_PATH_CHAIN_ONLY) return then_gate(launch_chain(p, ws, nv, stream));   // workspace left by an earlier call
     if (path == GDN_PATH_CHAIN_ONLY_T) return then_gate(launch_chain_t(p, ws, stream));
-    const int st = launch_prepare(p, ws, stream, !transposed);
+    const bool pairs = transposed && (Hv / Hq) % 2 == 0 && p.dbg != 3;
+    const int st = pairs ? launch_prepare_pair(p, ws, stream) : launch_prepare(p, ws, stream, !transposed);
     if (st != GDN_OK || path == GDN_PATH_PREPARE_ONLY || path == GDN_PATH_PREPARE_ONLY_T) return st;
     if (path == GDN_PATH_TWOPASS_T) return then_gate(launch_chain_t(p, ws, stream));
     return then_gate(launch_chain(p, ws, nv, stream));

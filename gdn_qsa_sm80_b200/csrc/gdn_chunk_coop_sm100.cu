@@ -987,7 +987,9 @@ int launch_coop_t(const Problem& p, const Workspace& ws, int* flags, size_t flag
     alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu, tus;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
     if (encode_workspace_maps(p, ws, &tw, &tp, &tus, &tu, NV)) return GDN_ERR_DRIVER;
-    if (cudaMemsetAsync(flags, skip_prepare ? 1 : 0, flag_bytes, stream) != cudaSuccess) return GDN_ERR_CUDA;
+    // p.dbg == 7 (test hook): chain roles only AND no flag raised, so that every chain CTA's wait for its first tile
+    // runs into the time limit, reports through the status word and returns
+    if (cudaMemsetAsync(flags, (skip_prepare && p.dbg != 7) ? 1 : 0, flag_bytes, stream) != cudaSuccess) return GDN_ERR_CUDA;
     using L = XSmem<NV>;
     const int n_chain = p.B * p.Hv * (kD / NV);
     const int grid = DEDICATED ? sm_count() : n_chain;

@@ -1,0 +1,304 @@
+// "prepare" for the transposed chain, two value heads at a time.
+//
+// The value heads that share a qk head (the reference's head mapping, csrc/gdn_chunk/gdn_kernel.cu:385-387) share
+// K, Q and therefore the raw products K K^T and Q K^T; only the gates differ.  One CTA of 256 threads prepares the
+// chunk of BOTH heads of a pair: one K / Q load and one [K;Q] K^T product for the two, then per head (one half of
+// the CTA each, in parallel) the decay mask, the 64 x 64 triangular inverse and T'' = T diag(beta), and finally ONE
+// product [T'_a ; T'_b] K (M = 128, no wasted rows) that yields W of both heads.  U is not formed: the transposed
+// chain computes U^T = V^T T''^T itself from the raw V tile.  Per head and chunk the workspace receives
+//   W [64][128] bf16,  P [64][64] bf16,  T'' [64][64] bf16 (at the start of the U array),  the per-token factors and
+//   the two scalars of the decay bound (sum of g, max beta |k|^2).
+// Same math and the same device helpers as gdn_prepare_kernel (gdn_chunk_prepare_sm100.cu), which remains the
+// producer for an odd number of value heads per qk head and for the kernels that read U from the workspace.
+// Stands in for the reference's gdn_prepare_kernel (csrc/gdn_chunk/gdn_kernel.cu:343-710).
+//
+// Two CTAs per SM (101 KB of shared memory, 128 TMEM columns, 128 registers each): 16 warps whose phases overlap.
+#include <cuda.h>
+
+#include "../../include/gdn_chunk_sm100.h"
+#include "gdn_common.cuh"
+#include "gdn_prep_device.cuh"
+#include "ptx_sm100.cuh"
+
+namespace gdn {
+namespace {
+
+struct QSmem {
+    static constexpr uint32_t KQ = 0;                    // [K;Q]: 2 k-halves x 128 rows x 128 B (K rows 0-63, Q rows 64-127)
+    static constexpr uint32_t YT = KQ + 8192;            // merge temporaries of head h at YT + h * 16384: Q's rows, dead after Q K^T
+    static constexpr uint32_t AS = KQ + 32768;           // A fp32 64 x 68 of head h at AS + h * 17408 ...
+    static constexpr uint32_t OP = AS;                   // ... then the stacked bf16 operand [T'_a ; T'_b] (16 KB) over head a's A
+    static constexpr uint32_t TM = AS + 2 * 17408;       // T fp32 64 x 68 of head h at TM + h * 17408 ...
+    static constexpr uint32_t STG = TM;                  // ... then the W staging tiles of both heads (32 KB)
+    static constexpr uint32_t kBytes = TM + 2 * 17408;   // 102400
+    static constexpr uint32_t kDynamic = kBytes + 1024;
+    static_assert(OP % 1024 == 0 && STG % 1024 == 0, "UMMA / TMA tiles must be 1024-byte aligned");
+};
+constexpr uint32_t kPairTmemCols = 128;   // [K;Q] K^T in the first 64, then W of both heads through all 128
+constexpr int kPairCtasPerSm = 2;
+
+template <bool GATE_F32>
+__global__ void __launch_bounds__(256, kPairCtasPerSm)
+gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                        const __grid_constant__ CUtensorMap tm_w, Problem p, Workspace ws, int NT, long long num_items) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t sm_u32 = smem_u32(sm);
+    __shared__ __align__(8) uint64_t bar_tma;
+    __shared__ __align__(8) uint64_t bar_mma;
+    __shared__ uint32_t tmem_slot;
+    __shared__ __align__(16) PrepScratch ps2[2];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = tid >> 7;                       // which head of the pair this half of the CTA prepares
+    const int htid = tid & 127, hwarp = htid >> 5, i = htid & 63;
+    const PrepCtx ctx{htid, 1 + h};               // the half's own thread numbering and named barrier
+    PrepScratch& ps = ps2[h];
+    const float scale0 = rsqrtf(static_cast<float>(kD));
+    const int rep = p.Hv / p.Hq, npairs = p.Hv / 2;
+    float* As = reinterpret_cast<float*>(sm + QSmem::AS + h * 17408);
+    float* Tm = reinterpret_cast<float*>(sm + QSmem::TM + h * 17408);
+    float* Yt = reinterpret_cast<float*>(sm + QSmem::YT + h * 16384);
+    uint8_t* kq = sm + QSmem::KQ;
+
+    // Persistent CTA: items L = blockIdx.x, blockIdx.x + gridDim.x, ...  L -> (b, chunk t, pair of value heads), the
+    // pair index fastest.
+    struct Item { int b, t, hv, hq, s0; size_t tile; };
+    auto decode = [&](long long L) {
+        Item x;
+        const int pr = static_cast<int>(L % npairs);
+        x.t = static_cast<int>((L / npairs) % NT);
+        x.b = static_cast<int>(L / (static_cast<long long>(npairs) * NT));
+        x.hv = 2 * pr + h;
+        x.hq = (2 * pr) / rep;
+        x.s0 = x.t * kChunk;
+        x.tile = (static_cast<size_t>(x.b) * p.Hv + x.hv) * NT + x.t;
+        return x;
+    };
+    auto issue_loads = [&](const Item& x) {   // one thread
+        mbar_arrive_expect_tx(&bar_tma, 4 * 8192);
+        tma_load_4d(kq + 0, &tm_k, &bar_tma, 0, x.hq, x.s0, x.b);
+        tma_load_4d(kq + 16384, &tm_k, &bar_tma, 64, x.hq, x.s0, x.b);
+        tma_load_4d(kq + 8192, &tm_q, &bar_tma, 0, x.hq, x.s0, x.b);
+        tma_load_4d(kq + 24576, &tm_q, &bar_tma, 64, x.hq, x.s0, x.b);
+    };
+
+    long long L = blockIdx.x;
+    Item cur = decode(L);
+    if (tid == 0) {
+        mbar_init(&bar_tma, 1);
+        mbar_init(&bar_mma, 1);
+        fence_mbar_init();
+        issue_loads(cur);
+    }
+    if (warp == 0) {
+        tmem_alloc(&tmem_slot, kPairTmemCols);
+        tmem_relinquish();
+    }
+    float gv, bv;
+    prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(cur.b) * p.S + cur.s0, cur.hv, p.Hv,
+                              min(kChunk, p.S - cur.s0), gv, bv, ctx, p.gate_act != 0);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t lane_base = static_cast<uint32_t>(hwarp) * 32u;   // (warp % 4) * 32: the warp's TMEM lane quadrant
+    uint32_t ph_tma = 0, ph_mma = 0;
+    bool ok = true;
+
+    for (; L < num_items && ok; L += gridDim.x) {
+        const size_t tile = cur.tile;
+        if (p.gate_act) prep_activate_gates(gv, bv);
+        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, ctx);
+        ctx.sync();
+
+        ok = mbar_wait(&bar_tma, ph_tma, p.status, kDevTimeoutTma);
+        ph_tma ^= 1;
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+
+        if (tid == 0) {   // raw K K^T (lanes 0-63) and Q K^T (lanes 64-127), shared by the two heads
+            tc_fence_after_sync();
+            constexpr uint32_t idesc = umma_idesc_bf16(128, 64, MAJOR_K, MAJOR_K);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint64_t ad = umma_smem_desc(sm_u32 + QSmem::KQ + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, SWZ_128B);
+                umma_bf16_ss(tmem, ad, ad, idesc, ks > 0);
+            }
+            umma_commit(&bar_mma);
+        }
+        if (p.l2norm) prep_l2norm_fold(ps, kq, ws.vec + tile * 256, ctx);   // while the UMMAs run
+        ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
+        ph_mma ^= 1;
+        // the previous item's W stores must have finished reading their staging tiles (the T buffers) before those are
+        // zeroed below
+        if (tid == 0) tma_store_wait_read();
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        prep_zero_upper_blocks(Tm, ctx);
+
+        tc_fence_after_sync();
+        {
+            float ri, diag[16];
+            if (p.l2norm) prep_row_setup_l2(ps, i, ri, diag);
+            else prep_row_setup(ps, i, ri, diag);
+            const float scale = p.l2norm ? scale0 * ps.rn[kChunk + i] : scale0;   // row factor of P
+            uint32_t r[32];
+            float f[32];
+            if (hwarp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
+                const float bi = p.l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
+                float ksq = 0.f;   // |k_i|^2: the diagonal of K K^T (for the decay bound of split sequences)
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
+                    prep_row_factors(ps, i, half, ri, diag, f);
+                    tmem_ld_wait();
+                    if (ws.meta && (i >> 5) == half) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (c == (i & 31)) ksq = __uint_as_float(r[c]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        float4 o;
+                        o.x = (half * 32 + c + 0 < i) ? bi * f[c + 0] * __uint_as_float(r[c + 0]) : 0.f;
+                        o.y = (half * 32 + c + 1 < i) ? bi * f[c + 1] * __uint_as_float(r[c + 1]) : 0.f;
+                        o.z = (half * 32 + c + 2 < i) ? bi * f[c + 2] * __uint_as_float(r[c + 2]) : 0.f;
+                        o.w = (half * 32 + c + 3 < i) ? bi * f[c + 3] * __uint_as_float(r[c + 3]) : 0.f;
+                        *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
+                    }
+                }
+                if (ws.meta) {   // max over the chunk of beta_i |k_i|^2, +inf when a gate is outside beta >= 0, g <= 0
+                    const float rk = p.l2norm ? ps.rn[i] : 1.f;
+                    const bool in_range = ps.bet[i] >= 0.f && ps.gam[i] <= (i > 0 ? ps.gam[i - 1] : 0.f);
+                    float bound = in_range ? ps.bet[i] * ksq * rk * rk : INFINITY;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, o));
+                    if (lane == 0) ps.wsum[hwarp] = bound;   // the cumsum's slots are free again by now
+                }
+            } else {           // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
+                __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
+                    prep_row_factors(ps, i, half, ri, diag, f);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint4 pk;
+                        pk.x = pack_bf16x2(scale * f[8 * ch + 0] * __uint_as_float(r[8 * ch + 0]), scale * f[8 * ch + 1] * __uint_as_float(r[8 * ch + 1]));
+                        pk.y = pack_bf16x2(scale * f[8 * ch + 2] * __uint_as_float(r[8 * ch + 2]), scale * f[8 * ch + 3] * __uint_as_float(r[8 * ch + 3]));
+                        pk.z = pack_bf16x2(scale * f[8 * ch + 4] * __uint_as_float(r[8 * ch + 4]), scale * f[8 * ch + 5] * __uint_as_float(r[8 * ch + 5]));
+                        pk.w = pack_bf16x2(scale * f[8 * ch + 6] * __uint_as_float(r[8 * ch + 6]), scale * f[8 * ch + 7] * __uint_as_float(r[8 * ch + 7]));
+                        *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
+                    }
+                }
+            }
+        }
+        tc_fence_before_sync();
+        ctx.sync();
+        if (ws.meta && htid == 0) {
+            ws.meta[2 * tile] = ps.gam[kChunk - 1] * (1.f / kLog2e);
+            ws.meta[2 * tile + 1] = fmaxf(ps.wsum[0], ps.wsum[1]);
+        }
+
+        prep_invert_unit_lower(As, Tm, Yt, ctx);
+
+        // both heads are done with their A matrices (the stacked operand lies over head a's) and with the raw
+        // products in tensor memory (W goes through the same columns)
+        __syncthreads();
+        if (htid < kChunk)   // T' = T diag(beta e^gamma): rows 64 h .. 64 h + 63 of the stacked operand
+            prep_store_scaled_T_row(Tm, ps.eg, i, sm + QSmem::OP, h * 64 + i);
+        else                 // T'' = T diag(beta), as it is, for the chain's V^T T''^T
+            prep_store_scaled_T_row_plain(Tm, ps.bet, i, ws.U + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
+        fence_proxy_async_smem();
+        __syncthreads();
+
+        if (tid == 0) {   // W of both heads: [T'_a ; T'_b] K
+            tc_fence_after_sync();
+            constexpr uint32_t idesc_w = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_MN);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint64_t ad = umma_smem_desc(sm_u32 + QSmem::OP + ks * 32, 16, 1024, SWZ_128B);
+                const uint64_t bk = umma_smem_desc(sm_u32 + QSmem::KQ + ks * 2048, 16384, 1024, SWZ_128B);
+                umma_bf16_ss(tmem, ad, bk, idesc_w, ks > 0);
+            }
+            umma_commit(&bar_mma);
+        }
+        ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
+        ph_mma ^= 1;
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+
+        // K, Q (the merge temporaries) and the operand are dead: the next item's loads and gate reads start now
+        const long long Ln = L + gridDim.x;
+        Item nxt = cur;
+        if (Ln < num_items) {
+            nxt = decode(Ln);
+            if (tid == 0) issue_loads(nxt);
+            prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(nxt.b) * p.S + nxt.s0, nxt.hv, p.Hv,
+                                      min(kChunk, p.S - nxt.s0), gv, bv, ctx, p.gate_act != 0);
+        }
+        {   // W rows -> bf16 -> swizzled staging tiles in the T buffers (T fp32 is dead).  TMEM lanes 0-63 are head a's
+            // rows, 64-127 head b's; warps 0-3 take columns 0-63, warps 4-7 columns 64-127.
+            const int hh = hwarp >> 1, row = (hwarp & 1) * 32 + lane, cpart = warp >> 2;
+            uint8_t* dst = sm + QSmem::STG + hh * 16384 + cpart * 8192;
+            uint32_t r[32];
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+                tmem_ld_x32(tmem_addr(tmem, lane_base, cpart * 64 + q2 * 32), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint4 pk;
+                    pk.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                    pk.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                    pk.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                    pk.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                    *reinterpret_cast<uint4*>(dst + swz_chunk_offset<128>(row, q2 * 4 + ch)) = pk;
+                }
+            }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncthreads();
+        if (tid == 0) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int row0 = static_cast<int>((tile + static_cast<size_t>(hh) * NT) * kChunk);   // tid 0 is in half 0: tile = head a's
+                tma_store_2d(&tm_w, sm + QSmem::STG + hh * 16384, 0, row0);
+                tma_store_2d(&tm_w, sm + QSmem::STG + hh * 16384 + 8192, 64, row0);
+            }
+            tma_store_commit();
+        }
+        cur = nxt;
+    }
+    if (tid == 0) tma_store_wait_all();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kPairTmemCols);
+}
+
+}  // namespace
+
+int launch_prepare_pair(const Problem& p, const Workspace& ws, cudaStream_t stream) {
+    if (p.Hv % 2 || (p.Hv / p.Hq) % 2) return GDN_ERR_BAD_ARGUMENT;
+    alignas(64) CUtensorMap tq, tk, tv, tw, tp;
+    if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
+    if (encode_workspace_maps(p, ws, &tw, &tp, nullptr, nullptr, 64)) return GDN_ERR_DRIVER;
+    const int NT = (p.S + kChunk - 1) / kChunk;
+    const long long items = static_cast<long long>(p.B) * (p.Hv / 2) * NT;
+    const long long max_ctas = static_cast<long long>(kPairCtasPerSm) * sm_count();
+    const unsigned grid = static_cast<unsigned>(items < max_ctas ? items : max_ctas);
+    auto go = [&](auto kernel) -> int {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, QSmem::kDynamic) != cudaSuccess)
+            return GDN_ERR_CUDA;
+        kernel<<<grid, 256, QSmem::kDynamic, stream>>>(tq, tk, tw, p, ws, NT, items);
+        count_launch();
+        return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
+    };
+    return p.gate_f32 ? go(gdn_prepare_pair_kernel<true>) : go(gdn_prepare_pair_kernel<false>);
+}
+
+}  // namespace gdn

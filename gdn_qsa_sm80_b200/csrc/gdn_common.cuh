@@ -92,6 +92,9 @@ int launch_fused(const Problem& p, int nv, cudaStream_t stream);
 // with_u = false (for the transposed chain): no U tile; T'' = T diag(beta), bf16 [tiles][64][64], is written at the
 // start of the U array instead.
 int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream, bool with_u = true);
+// The same as launch_prepare(with_u = false), two value heads of a qk head per CTA (shared K / Q load and raw
+// products, one product for both W); needs an even number of value heads per qk head.
+int launch_prepare_pair(const Problem& p, const Workspace& ws, cudaStream_t stream);
 int launch_chain(const Problem& p, const Workspace& ws, int nv, cudaStream_t stream);
 // The chain in transposed form: one CTA per (batch, value head), all 128 value columns (gdn_chain_t_device.cuh).
 // With ws.n_seg > 1 every sequence is cut into ws.n_seg segments that run as independent chains from a zero state,

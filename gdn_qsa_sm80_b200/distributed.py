@@ -183,6 +183,10 @@ def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, 
     serial ripple) and, once its incoming state has arrived, recomputes only the first p tokens.  A rank then does
     1 + p / S_seg passes instead of 3, and rank 0, whose incoming state is known from the start, always does one.
     Exact in fp32.
+
+    timeout_s: upper bound, in seconds, on every wait for a neighbour's boundary state.  A rank whose predecessor
+    has failed (raised before its send, left the job) then gets a RuntimeError from this call instead of waiting for
+    the process group's own, much longer, time-out; None waits as long as the process group does.
     """
     if compute is None:
         from .gdn_chunk_interface import gdn_chunk
@@ -198,7 +202,18 @@ def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, 
 
     def recv_state():
         buf = torch.empty(shape, dtype=torch.float32, device=dev)
-        dist.recv(buf, src=dist.get_global_rank(group, rank - 1) if group is not None else rank - 1, group=group)
+        src = dist.get_global_rank(group, rank - 1) if group is not None else rank - 1
+        if timeout_s is None:
+            dist.recv(buf, src=src, group=group)
+            return buf
+        import datetime
+        work = dist.irecv(buf, src=src, group=group)
+        try:
+            done = work.wait(timeout=datetime.timedelta(seconds=float(timeout_s)))
+        except RuntimeError as e:
+            raise RuntimeError(f"rank {rank}: no boundary state from rank {rank - 1} within {timeout_s} s") from e
+        if done is False:
+            raise RuntimeError(f"rank {rank}: no boundary state from rank {rank - 1} within {timeout_s} s")
         return buf
 
     def send_state(s):
@@ -246,7 +261,14 @@ def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, 
         _, a_seg = compute(q, k, torch.zeros_like(v), g, beta, eye)
     s_in = recv_state()             # the true states ripple down the ranks
     if forwards:
-        send_state(torch.matmul(a_seg.to(torch.float32), s_in) + b_seg.to(torch.float32))
+        if s_in.is_cuda:    # S_out = A_seg S_in + B_seg per (batch, head), fp32, by the library's scan kernel
+            from .gdn_chunk_interface import scan_transfers
+            n = B * Hv
+            _, s_out = scan_transfers(a_seg.to(torch.float32).reshape(n, 1, D, D), b_seg.to(torch.float32).reshape(n, 1, D, D),
+                                      s_in.reshape(n, D, D))
+            send_state(s_out.reshape(shape))
+        else:               # CPU ranks (host-logic tests)
+            send_state(torch.matmul(a_seg.to(torch.float32), s_in) + b_seg.to(torch.float32))
     # pass B: the segment from its true incoming state
     out, s_fin = compute(q, k, v, g, beta, s_in)
     return out, s_fin

@@ -166,3 +166,60 @@ def test_transfer_bound_premises():
     eye = torch.eye(128).expand(1, 2, 128, 128).contiguous()
     _, a = oracle_compute(q, k, torch.zeros_like(v), g, beta, eye)
     assert float(a.abs().max()) == 0.0
+
+
+def _failing_worker(rank, world, port, failure, q_out):
+    """Rank 0 fails on the host before it would send its boundary state; rank 1 must get an error, not wait."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    import datetime
+    import time
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        S = 128
+        q, k, v, g, beta, h0 = _problem(S)
+        lo, hi = segment_bounds(S, world)[rank]
+        seg = [t[:, lo:hi] for t in (q, k, v, g, beta)]
+
+        def compute(*a):
+            if rank == 0 and failure == "raises":
+                raise ValueError("injected failure before the send")
+            if rank == 0 and failure == "stalls":
+                time.sleep(8.0)             # far longer than the neighbour is willing to wait
+            return oracle_compute(*a)
+
+        t0 = time.time()
+        try:
+            sequence_parallel_forward(*seg, initial_state=h0, mode="pipeline", compute=compute, timeout_s=2.0)
+            q_out.put((rank, "ok", time.time() - t0))
+        except ValueError as e:
+            q_out.put((rank, "raised:" + str(e), time.time() - t0))
+        except RuntimeError as e:
+            q_out.put((rank, "timeout:" + str(e), time.time() - t0))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("failure", ["raises", "stalls"])
+def test_a_failed_neighbour_ends_the_wait_with_an_error(failure):
+    """Host-side failure detection of the sequence-parallel chain: a rank that raises before its send, or does not
+    send in time, makes its successor's bounded receive raise instead of blocking."""
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, failure, q_out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict()
+    for _ in range(2):
+        r = q_out.get(timeout=120)
+        results[r[0]] = r
+    for p in procs:
+        p.join(timeout=60)
+    assert results[1][1].startswith("timeout:") and "no boundary state from rank 0" in results[1][1]
+    assert results[1][2] < 7.0                        # the 2 s limit, not the process group's 60 s
+    assert results[0][1].startswith("raised:") if failure == "raises" else results[0][1] in ("ok",) or results[0][1].startswith("timeout:")

@@ -72,3 +72,34 @@ def test_prepare_outputs(S, workload):
     assert O.rel_l2(Ug, U) < 6e-3, O.rel_l2(Ug, U)
     assert O.rel_l2(vg[..., :129], vec[..., :129]) < 1e-5
     assert np.abs(Pg - P).max() < 2e-2 and np.abs(Ug - U).max() < 5e-2
+
+
+@pytest.mark.parametrize("S,workload,Hq,Hv", [(256, "default", 2, 4), (100, "default", 2, 4), (192, "long_context", 1, 4),
+                                               (128, "default", 3, 3)])
+def test_prepare_outputs_for_the_transposed_chain(S, workload, Hq, Hv):
+    """The producer of path "twopass_t": W, P, T'' = T diag(beta) (at the start of the U array) and the factors.
+    Two value heads per CTA when every qk head has an even number of them, else the one-head kernel without U."""
+    B = 2
+    q, k, v, g, beta, _ = make_inputs(workload, seed=11 + S, B=B, S=S, Hq=Hq, Hv=Hv)
+    dev = torch.device("cuda")
+    gdn_chunk(q.to(dev), k.to(dev), v.to(dev), g.to(dev), beta.to(dev), path="prepare_only_t")
+    iface.check_device_status(dev)
+    torch.cuda.synchronize()
+    off = (ctypes.c_size_t * 5)()
+    assert _lib.load().gdn_chunk_workspace_offsets(B, S, Hq, Hv, off) == 0
+    raw = iface._scratch[(torch.cuda.current_device(), torch.cuda.current_stream(dev).cuda_stream)]
+    NT = (S + 63) // 64
+    tiles = B * Hv * NT
+    Wg = raw[off[0]:off[0] + tiles * 16384].view(torch.bfloat16).float().cpu().numpy().reshape(B, Hv, NT, 64, 128)
+    Pg = raw[off[1]:off[1] + tiles * 8192].view(torch.bfloat16).float().cpu().numpy().reshape(B, Hv, NT, 64, 64)
+    T2g = raw[off[2]:off[2] + tiles * 8192].view(torch.bfloat16).float().cpu().numpy().reshape(B, Hv, NT, 64, 64)
+    vg = raw[off[3]:off[3] + tiles * 1024].view(torch.float32).cpu().numpy().reshape(B, Hv, NT, 256)
+    x = [t.float().numpy().astype(np.float64) for t in (q, k, v, g, beta)]
+    W, U, P, vec = numpy_prepare(*x)
+    assert O.rel_l2(Pg, P) < 4e-3, O.rel_l2(Pg, P)
+    assert O.rel_l2(Wg, W) < 6e-3, O.rel_l2(Wg, W)
+    assert O.rel_l2(vg[..., :129], vec[..., :129]) < 1e-5
+    # T'' V must reproduce U (V padded with zero rows like the kernel's tiles)
+    vv = x[2].transpose(0, 2, 1, 3)
+    vv = np.pad(vv, ((0, 0), (0, 0), (0, NT * 64 - S), (0, 0))).reshape(B, Hv, NT, 64, 128)
+    assert O.rel_l2(T2g @ vv, U) < 6e-3, O.rel_l2(T2g @ vv, U)
