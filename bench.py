@@ -225,7 +225,7 @@ def reference_arm(args, w, cfg, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     # the same share of the workload as the main arm; the reference's entry takes bf16 gates and has no initial state
     if args.workload == "default" or w.B < world:
@@ -524,7 +524,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="default", choices=["default", "short_batch", "throughput", "long_context"])
-    ap.add_argument("--path", default="auto", choices=["auto", "simt", "fused_nv64", "fused_nv32", "twopass_nv64", "twopass_nv32", "twopass_t", "coop", "coop_dedicated", "decode"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "twopass_nv64", "twopass_nv32", "twopass_t", "coop", "decode"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -564,7 +564,7 @@ def main():
     dev = torch.device("cuda", local_rank)
     affinity = bind_near_gpu(local_rank)                 # before the pinned host buffers are allocated
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")      # keep NCCL's version banner off stdout: one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # whatever NCCL logs: not on stdout (one JSON line only)
         dist.init_process_group("nccl", device_id=dev)
 
     if args.seq_parallel:
@@ -728,7 +728,7 @@ def main():
     # ---- the two kernels of a step timed on their own (CUDA events on the launching stream, L2 flushed) ----
     per_kernel = None
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
-    single_launch = args.path in ("coop", "coop_dedicated") or (args.path == "auto" and w.S <= 2048 and 4 * B_local * w.Hv <= n_sm)
+    single_launch = args.path == "coop" or (args.path == "auto" and w.S <= 2048 and 4 * B_local * w.Hv <= n_sm)
     transposed = args.path == "twopass_t" or (args.path == "auto" and not single_launch)
     kernels = ("gdn_coop_kernel (one launch)" if single_launch else
                "gdn_prepare_kernel + gdn_chain_t_kernel (sequences split on the device: segments, then their first chunks again)"

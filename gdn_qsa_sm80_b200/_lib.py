@@ -24,21 +24,18 @@ GATE_F32 = 1
 
 PATH_AUTO = 0
 PATH_SIMT = 1
-PATH_FUSED_NV64 = 2
-PATH_FUSED_NV32 = 3
 PATH_TWOPASS_NV64 = 4
 PATH_TWOPASS_NV32 = 5
 PATH_PREPARE_ONLY = 6
 PATH_CHAIN_ONLY = 7
 PATH_COOP = 8
 PATH_COOP_CHAIN_ONLY = 9
-PATH_COOP_DEDICATED = 10
 FLAG_QK_L2NORM = 1
 FLAG_GATE_ACTIVATIONS = 2
 
-PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "fused_nv64": PATH_FUSED_NV64, "fused_nv32": PATH_FUSED_NV32,
+PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, 
          "twopass_nv64": PATH_TWOPASS_NV64, "twopass_nv32": PATH_TWOPASS_NV32,
-         "prepare_only": PATH_PREPARE_ONLY, "chain_only": PATH_CHAIN_ONLY, "coop": PATH_COOP, "coop_chain_only": PATH_COOP_CHAIN_ONLY, "coop_dedicated": PATH_COOP_DEDICATED, "decode": 11, "twopass_t": 12,
+         "prepare_only": PATH_PREPARE_ONLY, "chain_only": PATH_CHAIN_ONLY, "coop": PATH_COOP, "coop_chain_only": PATH_COOP_CHAIN_ONLY, "decode": 11, "twopass_t": 12,
          "prepare_only_t": 13, "chain_only_t": 14}
 
 # Every symbol the public header declares (checked by the CPU tests).

@@ -133,10 +133,8 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
 #ifdef GDN_DIAGNOSTICS
     const bool tl_on = p.prof != nullptr && prof_cta && p.dbg >= 100 && lane == 0;
 #define GDN_TL(idx) if (tl_on && t == t0 + 20) p.prof[idx] = clock64();
-#define GDN_DIAG_ON(x) (x)
 #else
 #define GDN_TL(idx)
-#define GDN_DIAG_ON(x) false
 #endif
 
     if (warp == 12) {
@@ -175,7 +173,7 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
         constexpr uint32_t idesc_e1 = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_K, 1);    // negated A
         constexpr uint32_t idesc_e2 = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_MN);
         constexpr uint32_t idesc_e3 = umma_idesc_bf16(128, 64, MAJOR_K, MAJOR_K);
-        const bool prof = GDN_DIAG_ON(p.prof != nullptr && prof_cta);
+        const bool prof = GDN_DIAG(p.prof != nullptr && prof_cta);
         long long acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long ct = prof ? clock64() : 0;
 #define GDN_TPHASE(n)                                  \
@@ -257,7 +255,7 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
 
     if (warp >= 8) {
         // ------------------------------- output epilogue (warps 8-11) ----------------------------------------------
-        const bool oprof = GDN_DIAG_ON(p.prof != nullptr && prof_cta && tid == 256);
+        const bool oprof = GDN_DIAG(p.prof != nullptr && prof_cta && tid == 256);
         long long oacc[3] = {0, 0, 0};
         long long oct = oprof ? clock64() : 0;
 #define GDN_OPHASE(n)                                  \
@@ -370,7 +368,7 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
     publish_state();
 
     // optional cycle accounting by one critical thread of one CTA, summed over chunks
-    const bool cprof = GDN_DIAG_ON(p.prof != nullptr && prof_cta && tid == 0);
+    const bool cprof = GDN_DIAG(p.prof != nullptr && prof_cta && tid == 0);
     long long cacc[5] = {0, 0, 0, 0, 0};
     long long cct = cprof ? clock64() : 0;
 #define GDN_CPHASE(n)                                  \
@@ -446,6 +444,5 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
 }
 
 #undef GDN_TL
-#undef GDN_DIAG_ON
 }  // namespace chain_t
 }  // namespace gdn

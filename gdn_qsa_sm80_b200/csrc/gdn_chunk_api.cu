@@ -124,7 +124,7 @@ static size_t tiles_of(int B, int S, int Hv) {
 static bool path_uses_workspace(int path) {
     return path == GDN_PATH_AUTO || path == GDN_PATH_TWOPASS_NV64 || path == GDN_PATH_TWOPASS_NV32 ||
            path == GDN_PATH_PREPARE_ONLY || path == GDN_PATH_CHAIN_ONLY || path == GDN_PATH_COOP ||
-           path == GDN_PATH_COOP_CHAIN_ONLY || path == GDN_PATH_COOP_DEDICATED || path == GDN_PATH_TWOPASS_T ||
+           path == GDN_PATH_COOP_CHAIN_ONLY || path == GDN_PATH_TWOPASS_T ||
            path == GDN_PATH_PREPARE_ONLY_T || path == GDN_PATH_CHAIN_ONLY_T;
 }
 
@@ -184,12 +184,9 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
                    int gate_dtype, int path, unsigned flags, cudaStream_t stream, bool clear_status,
                    const OutputGate* gate) {
     if (flags & ~static_cast<unsigned>(GDN_FLAG_QK_L2NORM | GDN_FLAG_GATE_ACTIVATIONS)) return GDN_ERR_BAD_ARGUMENT;
-    // the first-generation fused kernel has neither option; every other path folds them into its prepare step
-    if (flags != 0 && (path == GDN_PATH_FUSED_NV64 || path == GDN_PATH_FUSED_NV32))
-        return GDN_ERR_BAD_ARGUMENT;
     if (B <= 0 || S < 0 || Hq <= 0 || Hv <= 0 || Hv % Hq != 0) return GDN_ERR_BAD_ARGUMENT;
     if (gate_dtype != GDN_GATE_BF16 && gate_dtype != GDN_GATE_F32) return GDN_ERR_BAD_ARGUMENT;
-    if (path < GDN_PATH_AUTO || path > GDN_PATH_CHAIN_ONLY_T) return GDN_ERR_BAD_ARGUMENT;
+    if (path < GDN_PATH_AUTO || path > GDN_PATH_CHAIN_ONLY_T || path == 2 || path == 3 || path == 10) return GDN_ERR_BAD_ARGUMENT;
     // the least a path needs; gdn_chunk_scratch_bytes may ask for more (room to split long sequences), which is used
     // when it is there
     const size_t need = path_uses_workspace(path) ? workspace_layout(tiles_of(B, S, Hv)).total : 256;
@@ -240,8 +237,6 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     if (path == GDN_PATH_DECODE || (path == GDN_PATH_AUTO && S <= kDecodeMaxTokens))
         return then_gate(launch_decode(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA);
     if (path == GDN_PATH_SIMT) return then_gate(launch_simt(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA);
-    if (path == GDN_PATH_FUSED_NV64) return then_gate(launch_fused(p, 64, stream));
-    if (path == GDN_PATH_FUSED_NV32) return then_gate(launch_fused(p, 32, stream));
     // Automatic choice, by shape alone.  Few short sequences: the single-launch kernel whose four 32-column CTAs per
     // head share the prepare work (2048 tokens, 32 sequences: 0.080 ms).  Everything else: the prepare kernel and the
     // transposed chain (one CTA per head, state-dependent operands in tensor memory), which splits long sequences
@@ -269,8 +264,6 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     ws.meta = seg_states ? reinterpret_cast<float*>(base + l.meta) : nullptr;
     ws.seg_state = seg_states ? reinterpret_cast<float*>(base + l.seg_state) : nullptr;
     ws.n_seg = seg_states ? static_cast<int>(seg_states / (static_cast<size_t>(B) * Hv)) : 1;
-    if (path == GDN_PATH_COOP_DEDICATED)
-        return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, false, true));
     if (path == GDN_PATH_COOP_CHAIN_ONLY)
         return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, true));
     if (path == GDN_PATH_COOP) {

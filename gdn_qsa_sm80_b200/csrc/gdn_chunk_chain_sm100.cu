@@ -243,7 +243,7 @@ gdn_chain_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         };
 
         // optional cycle accounting by the UMMA-issuing thread of CTA (0,0,0), summed over chunks
-        const bool prof_on = p.prof != nullptr && issuer && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        const bool prof_on = GDN_DIAG(p.prof != nullptr && issuer && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
         long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
         long long prof_t = prof_on ? clock64() : 0;
 #define GDN_PHASE(n)                                   \

@@ -11,15 +11,10 @@
 // the chain's latency instead of preceding it as a separate kernel, and the workspace is consumed from L2
 // microseconds after it is written.
 //
-// Two arrangements of the roles:
-//   DEDICATED = false  NV = 32.  Every CTA is a chain CTA (4 per head) plus one prepare group that prepares every
-//                      fourth chunk of its own head.  12 warps: 0-3 chain epilogues (warp 2 lane 0 issues D3/D5),
-//                      4 TMA producer, 5 issues D4, 6 publisher, 8-11 prepare group.  Needs 4*B*Hv <= #SMs.
-//   DEDICATED = true   NV = 64.  CTAs [0, n_chain) are chain CTAs (2 per head: warps 0-7 epilogues in two groups of
-//                      32 columns, 8 TMA producer, 9 issues D4); the remaining CTAs hold three slim prepare groups
-//                      each (warps 0-3, 4-7, 8-11; 71 KB and 128 TMEM columns per group, thread 0 of a group is
-//                      its publisher) and walk the tiles chunk-major (every head's chunk 0, then chunk 1, ...), so
-//                      the chain shares its SM with nobody.  Needs 2*B*Hv plus a few CTAs <= #SMs.
+// Roles: NV = 32.  Every CTA is a chain CTA (4 per head) plus one prepare group that prepares every fourth chunk
+// of its own head.  12 warps: 0-3 chain epilogues (warp 2 lane 0 issues D3/D5), 4 TMA producer, 5 issues D4,
+// 6 publisher, 8-11 prepare group.  Needs 4*B*Hv <= #SMs.  Used for short sequences (up to 2048 tokens); longer ones
+// and larger batches take the prepare kernel and the transposed chain.
 //
 // All CTAs must be resident together (one CTA per SM because of its shared memory): the kernel is launched
 // cooperatively, so the runtime refuses a grid that cannot be resident at once and schedules it as a whole.
@@ -168,7 +163,7 @@ __device__ __forceinline__ void prepare_role(const PrepRes& r, int ptid, const C
                                   min(kChunk, p.S - t * kChunk), gv, bv, ctx, p.gate_act != 0);
     };
     // optional cycle accounting by thread 0 of one prepare group, summed over its tiles
-    const bool prof_on = p.prof != nullptr && ptid == 0 && prof_cta;
+    const bool prof_on = GDN_DIAG(p.prof != nullptr && ptid == 0 && prof_cta);
     long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     long long prof_t = prof_on ? clock64() : 0, prof_n = 0;
 #define GDN_PHASE(n)                                   \
@@ -341,270 +336,6 @@ __device__ __forceinline__ void prepare_role(const PrepRes& r, int ptid, const C
     }
 }
 
-// ------------------------------------------------------------------------------------------------------
-// The same prepare steps for a group that shares its CTA with two others: 128 TMEM columns instead of 256 (W and
-// U one after the other), and no publisher thread - thread 0 of the group issues the TMA stores of a tile and
-// raises the tile's flag one tile later, when waiting for the stores' completion costs nothing.
-// ------------------------------------------------------------------------------------------------------
-template <bool GATE_F32>
-__device__ __forceinline__ void prepare_role_slim(const PrepRes& r, int ptid, const CUtensorMap* tm_q, const CUtensorMap* tm_k,
-                                                  const CUtensorMap* tm_v, const CUtensorMap* tm_w, const CUtensorMap* tm_us,
-                                                  const Problem& p, const Workspace& ws, int* flags,
-                                                  const TileSched& sched, volatile int* abortp, bool prof_cta) {
-    const PrepCtx ctx{ptid, r.bar_id};
-    PrepScratch& ps = *r.ps;
-    const int pwarp = ptid >> 5, i = ptid & 63;
-    const uint32_t lane_base = static_cast<uint32_t>(pwarp) * 32u;
-    const float scale0 = rsqrtf(static_cast<float>(kD));
-    const int NT = sched.NT, rep = p.Hv / p.Hq;
-    float* As = reinterpret_cast<float*>(r.sm + PAS);
-    float* Tm = reinterpret_cast<float*>(r.sm + PTM);
-    float* Yt = reinterpret_cast<float*>(r.sm + PYT);
-    uint8_t* kq = r.sm + PKQ;
-    const uint32_t kq_u32 = r.sm_u32 + PKQ, ts_u32 = r.sm_u32 + PAS;
-    const uint32_t tm_prep = r.tmem;
-    uint32_t ph_tma = 0, ph_mma = 0;
-    long long prev_tile = -1;   // thread 0: the tile whose W / U stores are in flight and whose flag is still to be raised
-
-    auto issue_kq = [&](int b, int hv, int t) {   // one thread
-        const int hq = hv / rep;
-        mbar_arrive_expect_tx(r.tma, 4 * 8192);
-        tma_load_4d(kq + 0, tm_k, r.tma, 0, hq, t * kChunk, b);
-        tma_load_4d(kq + 16384, tm_k, r.tma, 64, hq, t * kChunk, b);
-        tma_load_4d(kq + 8192, tm_q, r.tma, 0, hq, t * kChunk, b);
-        tma_load_4d(kq + 24576, tm_q, r.tma, 64, hq, t * kChunk, b);
-    };
-    auto load_gates = [&](int b, int hv, int t, float& gv, float& bv) {
-        prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(b) * p.S + t * kChunk, hv, p.Hv,
-                                  min(kChunk, p.S - t * kChunk), gv, bv, ctx, p.gate_act != 0);
-    };
-    // optional cycle accounting by thread 0 of one prepare group, summed over its tiles
-    const bool prof_on = p.prof != nullptr && ptid == 0 && prof_cta;
-    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long prof_t = prof_on ? clock64() : 0, prof_n = 0;
-#define GDN_PHASE(n)                                   \
-    if (prof_on) {                                     \
-        const long long now_ = clock64();              \
-        prof_acc[n] += now_ - prof_t;                  \
-        prof_t = now_;                                 \
-    }
-    int b, hv, t;
-    float gv = 0.f, bv = 0.f;
-    bool have = sched.get(0, b, hv, t);
-    if (have) {
-        if (ptid == 0) issue_kq(b, hv, t);
-        load_gates(b, hv, t, gv, bv);
-    }
-    for (long long n = 0; have; ++n) {
-        const size_t tile = (static_cast<size_t>(b) * p.Hv + hv) * NT + t;
-        int bn, hvn, tn;
-        const bool have_next = sched.get(n + 1, bn, hvn, tn);
-        if (p.gate_act) prep_activate_gates(gv, bv);
-        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, ctx);
-        ctx.sync();
-        GDN_PHASE(0)
-        mbar_wait_abortable(r.tma, ph_tma, p.status, kTimeoutPrepTma, abortp);
-        ph_tma ^= 1;
-        GDN_PHASE(1)
-        if (ptid == 0) {   // raw K K^T (lanes 0-63) and Q K^T (lanes 64-127)
-            tc_fence_after_sync();
-            constexpr uint32_t idesc = umma_idesc_bf16(128, 64, MAJOR_K, MAJOR_K);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                const uint64_t ad = umma_smem_desc(kq_u32 + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, SWZ_128B);
-                umma_bf16_ss(tm_prep, ad, ad, idesc, ks > 0);
-            }
-            umma_commit(r.mma);
-        }
-        if (p.l2norm) prep_l2norm_fold(ps, kq, ws.vec + tile * 256, ctx);   // while the UMMAs run
-        mbar_wait_abortable(r.mma, ph_mma, p.status, kTimeoutPrepMma, abortp);
-        ph_mma ^= 1;
-        tc_fence_after_sync();
-        GDN_PHASE(2)
-        if (ptid == 0) {   // Q is no longer needed: V takes its place (two 64-column groups, 16 KB apart)
-            mbar_arrive_expect_tx(r.tma, 2 * 8192);
-            tma_load_4d(kq + 8192, tm_v, r.tma, 0, hv, t * kChunk, b);
-            tma_load_4d(kq + 24576, tm_v, r.tma, 64, hv, t * kChunk, b);
-        }
-        // next tile's gates: a strided global read, issued a whole tile ahead so its latency never shows
-        // (this tile's values were consumed by prep_gates above)
-        if (have_next) load_gates(bn, hvn, tn, gv, bv);
-        // the previous tile's W / U staging tiles (the T and A buffers) must have been read by its TMA stores before
-        // they are zeroed / overwritten below
-        if (ptid == 0) tma_store_wait_read();
-        ctx.sync();
-        prep_zero_upper_blocks(Tm, ctx);
-        {
-            float ri, diag[16];
-            if (p.l2norm) prep_row_setup_l2(ps, i, ri, diag);
-            else prep_row_setup(ps, i, ri, diag);
-            const float scale = p.l2norm ? scale0 * ps.rn[kChunk + i] : scale0;   // row factor of P
-            uint32_t rr[32];
-            float f[32];
-            if (pwarp < 2) {
-                const float bi = p.l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    tmem_ld_x32(tmem_addr(tm_prep, lane_base, half * 32), rr);
-                    prep_row_factors(ps, i, half, ri, diag, f);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        float4 o;
-                        o.x = (half * 32 + c + 0 < i) ? bi * f[c + 0] * __uint_as_float(rr[c + 0]) : 0.f;
-                        o.y = (half * 32 + c + 1 < i) ? bi * f[c + 1] * __uint_as_float(rr[c + 1]) : 0.f;
-                        o.z = (half * 32 + c + 2 < i) ? bi * f[c + 2] * __uint_as_float(rr[c + 2]) : 0.f;
-                        o.w = (half * 32 + c + 3 < i) ? bi * f[c + 3] * __uint_as_float(rr[c + 3]) : 0.f;
-                        *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
-                    }
-                }
-            } else {
-                __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    tmem_ld_x32(tmem_addr(tm_prep, lane_base, half * 32), rr);
-                    prep_row_factors(ps, i, half, ri, diag, f);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint4 pk;
-                        pk.x = pack_bf16x2(scale * f[8 * ch + 0] * __uint_as_float(rr[8 * ch + 0]), scale * f[8 * ch + 1] * __uint_as_float(rr[8 * ch + 1]));
-                        pk.y = pack_bf16x2(scale * f[8 * ch + 2] * __uint_as_float(rr[8 * ch + 2]), scale * f[8 * ch + 3] * __uint_as_float(rr[8 * ch + 3]));
-                        pk.z = pack_bf16x2(scale * f[8 * ch + 4] * __uint_as_float(rr[8 * ch + 4]), scale * f[8 * ch + 5] * __uint_as_float(rr[8 * ch + 5]));
-                        pk.w = pack_bf16x2(scale * f[8 * ch + 6] * __uint_as_float(rr[8 * ch + 6]), scale * f[8 * ch + 7] * __uint_as_float(rr[8 * ch + 7]));
-                        *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
-                    }
-                }
-            }
-        }
-        tc_fence_before_sync();
-        ctx.sync();
-        // thread 0 is its group's publisher: the previous tile's stores were issued about 8 k cycles ago, so waiting
-        // for their completion costs little by now; then that tile's flag goes up
-        if (ptid == 0 && prev_tile >= 0) {
-            tma_store_wait_all();
-            fence_proxy_async_all();
-            __threadfence();     // cumulative: also covers the group's P / factor stores of that tile
-            if (!*abortp) st_release_gpu(flags + prev_tile, 1);
-            prev_tile = -1;
-        }
-        GDN_PHASE(3)
-        prep_invert_unit_lower(As, Tm, Yt, ctx);
-        GDN_PHASE(4)
-        {   // A is dead: its buffer receives the bf16 operand [T diag(beta e^gamma) ; T diag(beta)]
-            const int which = ptid >> 6;
-            prep_store_scaled_T_row(Tm, which == 0 ? ps.eg : ps.bet, i, r.sm + PAS, which * 64 + i);
-        }
-        fence_proxy_async_smem();
-        ctx.sync();
-        mbar_wait_abortable(r.tma, ph_tma, p.status, kTimeoutPrepTma, abortp);   // V has landed
-        ph_tma ^= 1;
-        GDN_PHASE(5)
-        // W = T' K and U = T'' V go through the same 128 TMEM columns one after the other (both products use the
-        // stacked operand [T';T'']: rows 0-63 of the first are W, rows 64-127 of the second are U)
-        constexpr uint32_t idesc_wu = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_MN);
-        if (ptid == 0) {
-            tc_fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                const uint64_t ad = umma_smem_desc(ts_u32 + ks * 32, 16, 1024, SWZ_128B);
-                const uint64_t bk = umma_smem_desc(kq_u32 + ks * 2048, 16384, 1024, SWZ_128B);
-                umma_bf16_ss(tm_prep, ad, bk, idesc_wu, ks > 0);
-            }
-            umma_commit(r.mma);
-        }
-        mbar_wait_abortable(r.mma, ph_mma, p.status, kTimeoutPrepMma, abortp);
-        ph_mma ^= 1;
-        tc_fence_after_sync();
-        if (pwarp < 2) {   // W rows -> bf16 -> staging tile in the T buffer (T fp32 is dead)
-            uint32_t rr[32];
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                tmem_ld_x32(tmem_addr(tm_prep, lane_base, q4 * 32), rr);
-                tmem_ld_wait();
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint4 pk;
-                    pk.x = pack_bf16x2(__uint_as_float(rr[8 * ch + 0]), __uint_as_float(rr[8 * ch + 1]));
-                    pk.y = pack_bf16x2(__uint_as_float(rr[8 * ch + 2]), __uint_as_float(rr[8 * ch + 3]));
-                    pk.z = pack_bf16x2(__uint_as_float(rr[8 * ch + 4]), __uint_as_float(rr[8 * ch + 5]));
-                    pk.w = pack_bf16x2(__uint_as_float(rr[8 * ch + 6]), __uint_as_float(rr[8 * ch + 7]));
-                    *reinterpret_cast<uint4*>(r.sm + PTM + (q4 >> 1) * 8192 + swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
-                }
-            }
-        }
-        tc_fence_before_sync();
-        ctx.sync();               // W has left the accumulator
-        if (ptid == 0) {
-            tc_fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                const uint64_t ad = umma_smem_desc(ts_u32 + ks * 32, 16, 1024, SWZ_128B);
-                const uint64_t bv_ = umma_smem_desc(kq_u32 + 8192 + ks * 2048, 16384, 1024, SWZ_128B);
-                umma_bf16_ss(tm_prep, ad, bv_, idesc_wu, ks > 0);
-            }
-            umma_commit(r.mma);
-        }
-        mbar_wait_abortable(r.mma, ph_mma, p.status, kTimeoutPrepMma, abortp);
-        ph_mma ^= 1;
-        tc_fence_after_sync();
-        GDN_PHASE(6)
-        // the tile's K/V buffer and the [T';T''] operand are free: next tile's K and Q
-        if (have_next && ptid == 0) issue_kq(bn, hvn, tn);
-        if (pwarp >= 2) {   // U rows -> staging tile in the A buffer (the operand there is dead)
-            uint32_t rr[32];
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                tmem_ld_x32(tmem_addr(tm_prep, lane_base, q4 * 32), rr);
-                tmem_ld_wait();
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint4 pk;
-                    pk.x = pack_bf16x2(__uint_as_float(rr[8 * ch + 0]), __uint_as_float(rr[8 * ch + 1]));
-                    pk.y = pack_bf16x2(__uint_as_float(rr[8 * ch + 2]), __uint_as_float(rr[8 * ch + 3]));
-                    pk.z = pack_bf16x2(__uint_as_float(rr[8 * ch + 4]), __uint_as_float(rr[8 * ch + 5]));
-                    pk.w = pack_bf16x2(__uint_as_float(rr[8 * ch + 6]), __uint_as_float(rr[8 * ch + 7]));
-                    *reinterpret_cast<uint4*>(r.sm + PAS + (q4 >> 1) * 8192 + swz_chunk_offset<128>(i, (q4 & 1) * 4 + ch)) = pk;
-                }
-            }
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        ctx.sync();
-        if (ptid == 0) {   // this tile's stores; its flag is raised in the middle of the next tile (or after the loop)
-            const int row0 = static_cast<int>(tile * kChunk);
-            tma_store_2d(tm_w, r.sm + PTM, 0, row0);
-            tma_store_2d(tm_w, r.sm + PTM + 8192, 64, row0);
-            tma_store_2d(tm_us, r.sm + PAS, 0, row0);
-            tma_store_2d(tm_us, r.sm + PAS + 8192, 64, row0);
-            tma_store_commit();
-            prev_tile = static_cast<long long>(tile);
-            if (n == 0) {   // the chains are waiting for the very first tiles: publish this one at once
-                tma_store_wait_all();
-                fence_proxy_async_all();
-                __threadfence();
-                if (!*abortp) st_release_gpu(flags + prev_tile, 1);
-                prev_tile = -1;
-            }
-        }
-        GDN_PHASE(7)
-        ++prof_n;
-        have = have_next;
-        b = bn; hv = hvn; t = tn;
-    }
-#undef GDN_PHASE
-    if (ptid == 0 && prev_tile >= 0) {   // the last tile's stores and flag
-        tma_store_wait_all();
-        fence_proxy_async_all();
-        __threadfence();
-        if (!*abortp) st_release_gpu(flags + prev_tile, 1);
-    }
-    if (prof_on) {
-        for (int n = 0; n < 8; ++n) p.prof[n] = prof_acc[n];
-        p.prof[15] = prof_n;
-    }
-}
-
 // Publisher of one prepare group (one thread): stores W and U from the staging tiles, frees the tiles, and raises the
 // tile's flag once the stores are complete; on its own thread the ~3 us write latency stays off the prepare group.
 __device__ __forceinline__ void publisher_role(const PrepRes& r, const CUtensorMap* tm_w, const CUtensorMap* tm_us,
@@ -763,7 +494,7 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
     };
 
     // optional cycle accounting by the UMMA-issuing thread of one chain CTA, summed over chunks
-    const bool cprof = p.prof != nullptr && issuer && prof_cta;
+    const bool cprof = GDN_DIAG(p.prof != nullptr && issuer && prof_cta);
     long long cacc[7] = {0, 0, 0, 0, 0, 0, 0};
     long long ct = 0;
 #define GDN_CPHASE(n)                                  \
@@ -881,13 +612,12 @@ __device__ __forceinline__ void chain_roles(uint8_t* sm, uint32_t sm_u32, uint32
     }
 }
 
-template <int NV, bool DEDICATED, bool GATE_F32>
+template <int NV, bool GATE_F32>
 __global__ void __launch_bounds__(384, 1)
 gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
                 const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_u,
-                const __grid_constant__ CUtensorMap tm_us, Problem p, Workspace ws, int* flags, int skip_prepare,
-                int n_chain) {
+                const __grid_constant__ CUtensorMap tm_us, Problem p, Workspace ws, int* flags, int skip_prepare) {
     using L = XSmem<NV>;
     constexpr int kSplits = kD / NV;
     extern __shared__ uint8_t smem_raw[];
@@ -898,16 +628,15 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __shared__ __align__(8) uint64_t bar_empty[STAGES];
     __shared__ __align__(8) uint64_t bar_d3, bar_kv, bar_vn;
     __shared__ __align__(8) uint64_t bar_pv[2];
-    __shared__ __align__(8) uint64_t bar_prep[3][4];   // per prepare group: tma, mma, ready, free
+    __shared__ __align__(8) uint64_t bar_prep[1][4];   // the prepare group's barriers: tma, mma, ready, free
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ __align__(16) PrepScratch ps[3];
+    __shared__ __align__(16) PrepScratch ps[1];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NT = (p.S + kChunk - 1) / kChunk;
     const int bid = blockIdx.x;
-    const bool chain_cta = !DEDICATED || bid < n_chain;
-    const int head = bid / kSplits, split = bid % kSplits;      // meaningful for chain CTAs
+    const int head = bid / kSplits, split = bid % kSplits;
     const int hv = head % p.Hv, b = head / p.Hv;
 
     if (tid == 0) {
@@ -920,8 +649,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_init(&bar_vn, 1);
         mbar_init(&bar_pv[0], 1);
         mbar_init(&bar_pv[1], 1);
-        for (int gi = 0; gi < 3; ++gi)
-            for (int k = 0; k < 4; ++k) mbar_init(&bar_prep[gi][k], 1);
+        for (int k = 0; k < 4; ++k) mbar_init(&bar_prep[0][k], 1);
         abort_flag = 0;
         fence_mbar_init();
     }
@@ -946,31 +674,15 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         return r;
     };
 
-    if (!DEDICATED) {
-        // every CTA: chain roles on warps 0-5, publisher on warp 6, one prepare group on warps 8-11
-        if (warp < 4 * (NV / 32) + 2) {
-            ChainBars cb{bar_full, bar_empty, &bar_d3, &bar_kv, &bar_vn, bar_pv};
-            chain_roles<NV>(sm, sm_u32, tmem, cb, &tm_q, &tm_k, &tm_w, &tm_p, &tm_u, p, ws, flags, abortp, split, hv, b, bid == 0);
-        } else if (!skip_prepare && (warp == 6 || warp >= 8)) {
-            const PrepRes r = prep_res(0, L::kChainBytes, 256);
-            const TileSched sched{split, kSplits, 1, b, hv, NT, p.B * p.Hv, p.Hv};
-            if (warp >= 8) prepare_role<GATE_F32>(r, tid - 256, &tm_q, &tm_k, &tm_v, p, ws, sched, abortp, bid == 0);
-            else if (lane == 0) publisher_role(r, &tm_w, &tm_us, p, flags, sched, abortp);
-        }
-    } else if (chain_cta) {
-        if (warp < 4 * (NV / 32) + 2) {
-            ChainBars cb{bar_full, bar_empty, &bar_d3, &bar_kv, &bar_vn, bar_pv};
-            chain_roles<NV>(sm, sm_u32, tmem, cb, &tm_q, &tm_k, &tm_w, &tm_p, &tm_u, p, ws, flags, abortp, split, hv, b, bid == 0);
-        }
-    } else if (!skip_prepare) {
-        // prepare CTA: three slim groups on warps 0-3, 4-7 and 8-11 (71 KB of shared memory and 128 TMEM columns each),
-        // every group its own publisher; tiles chunk-major (every head's chunk 0, then chunk 1, ...)
-        const int n_prep = static_cast<int>(gridDim.x) - n_chain;
-        const int gi = warp >> 2;
-        const PrepRes r = prep_res(gi, gi * kPrepBytes, gi * 128);
-        const TileSched sched{static_cast<long long>(bid - n_chain) * 3 + gi, 3ll * n_prep, 0, 0, 0, NT, p.B * p.Hv, p.Hv};
-        prepare_role_slim<GATE_F32>(r, tid & 127, &tm_q, &tm_k, &tm_v, &tm_w, &tm_us, p, ws, flags, sched, abortp,
-                                    bid == n_chain && gi == 0);
+    // every CTA: chain roles on warps 0-5, publisher on warp 6, one prepare group on warps 8-11
+    if (warp < 4 * (NV / 32) + 2) {
+        ChainBars cb{bar_full, bar_empty, &bar_d3, &bar_kv, &bar_vn, bar_pv};
+        chain_roles<NV>(sm, sm_u32, tmem, cb, &tm_q, &tm_k, &tm_w, &tm_p, &tm_u, p, ws, flags, abortp, split, hv, b, bid == 0);
+    } else if (!skip_prepare && (warp == 6 || warp >= 8)) {
+        const PrepRes r = prep_res(0, L::kChainBytes, 256);
+        const TileSched sched{split, kSplits, 1, b, hv, NT, p.B * p.Hv, p.Hv};
+        if (warp >= 8) prepare_role<GATE_F32>(r, tid - 256, &tm_q, &tm_k, &tm_v, p, ws, sched, abortp, bid == 0);
+        else if (lane == 0) publisher_role(r, &tm_w, &tm_us, p, flags, sched, abortp);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -982,7 +694,7 @@ gdn_coop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
-template <int NV, bool DEDICATED>
+template <int NV>
 int launch_coop_t(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream, bool skip_prepare) {
     alignas(64) CUtensorMap tq, tk, tv, tw, tp, tu, tus;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
@@ -991,10 +703,8 @@ int launch_coop_t(const Problem& p, const Workspace& ws, int* flags, size_t flag
     // runs into the time limit, reports through the status word and returns
     if (cudaMemsetAsync(flags, (skip_prepare && p.dbg != 7) ? 1 : 0, flag_bytes, stream) != cudaSuccess) return GDN_ERR_CUDA;
     using L = XSmem<NV>;
-    const int n_chain = p.B * p.Hv * (kD / NV);
-    const int grid = DEDICATED ? sm_count() : n_chain;
-    const uint32_t smem = (DEDICATED ? (L::kChainBytes > 3 * kPrepBytes ? L::kChainBytes : 3 * kPrepBytes)
-                                     : L::kChainBytes + kPrepBytes) + 1024;
+    const int grid = p.B * p.Hv * (kD / NV);
+    const uint32_t smem = L::kChainBytes + kPrepBytes + 1024;
     auto go = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return GDN_ERR_CUDA;
         // Cooperative launch: the CTAs wait on flags raised by other CTAs of the same grid, so all of them must be
@@ -1010,7 +720,7 @@ int launch_coop_t(const Problem& p, const Workspace& ws, int* flags, size_t flag
         attr[0].val.cooperative = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tq, tk, tv, tw, tp, tu, tus, p, ws, flags, skip_prepare ? 1 : 0, n_chain);
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tq, tk, tv, tw, tp, tu, tus, p, ws, flags, skip_prepare ? 1 : 0);
         if (e != cudaSuccess) {
             (void)cudaGetLastError();
             return GDN_ERR_CUDA;
@@ -1018,28 +728,19 @@ int launch_coop_t(const Problem& p, const Workspace& ws, int* flags, size_t flag
         count_launch();
         return GDN_OK;
     };
-    return p.gate_f32 ? go(gdn_coop_kernel<NV, DEDICATED, true>) : go(gdn_coop_kernel<NV, DEDICATED, false>);
+    return p.gate_f32 ? go(gdn_coop_kernel<NV, true>) : go(gdn_coop_kernel<NV, false>);
 }
 
 }  // namespace
 
-// in-CTA arrangement: four chain CTAs per head, each with a prepare group
+// four chain CTAs per head, each with a prepare group
 bool coop_supported(const Problem& p) {
     return static_cast<long long>(p.B) * p.Hv * 4 <= sm_count();
 }
-// dedicated arrangement: two chain CTAs per head plus at least a quarter of the SMs for prepare CTAs
-bool coop_dedicated_supported(const Problem& p) {
-    return static_cast<long long>(p.B) * p.Hv * 2 * 4 <= 3ll * sm_count();
-}
 
-int launch_coop(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream, bool skip_prepare,
-                bool dedicated) {
-    if (dedicated) {
-        if (!coop_dedicated_supported(p)) return GDN_ERR_BAD_ARGUMENT;
-        return launch_coop_t<64, true>(p, ws, flags, flag_bytes, stream, skip_prepare);
-    }
+int launch_coop(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream, bool skip_prepare) {
     if (!coop_supported(p)) return GDN_ERR_BAD_ARGUMENT;
-    return launch_coop_t<32, false>(p, ws, flags, flag_bytes, stream, skip_prepare);
+    return launch_coop_t<32>(p, ws, flags, flag_bytes, stream, skip_prepare);
 }
 
 }  // namespace gdn

@@ -88,7 +88,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     };
 
     // optional cycle accounting by thread 0 of CTA 0, summed over its tiles (slot 15 counts the tiles)
-    const bool prof_on = p.prof != nullptr && tid == 0 && blockIdx.x == 0;
+    const bool prof_on = GDN_DIAG(p.prof != nullptr && tid == 0 && blockIdx.x == 0);
     long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     long long prof_t = prof_on ? clock64() : 0;
 #define GDN_PHASE(n)                                   \

@@ -7,6 +7,14 @@
 #include <stddef.h>
 #include <stdint.h>
 
+// The kernels' cycle accounting is compiled in only with -DGDN_DIAGNOSTICS; otherwise every "is accounting on"
+// test is the constant false and the accounting code disappears from the kernels.
+#ifdef GDN_DIAGNOSTICS
+#define GDN_DIAG(x) (x)
+#else
+#define GDN_DIAG(x) false
+#endif
+
 namespace gdn {
 
 constexpr int kD = 128;      // head dimension (keys and values)
@@ -84,9 +92,6 @@ void count_launch();
 // Token-by-token fp32 kernel on CUDA cores (one CTA per (batch, value head)).
 cudaError_t launch_simt(const Problem& p, cudaStream_t stream);
 
-// Fused tcgen05 kernel; nv = value columns per CTA (32 or 64).  Returns a GDN_* status.
-int launch_fused(const Problem& p, int nv, cudaStream_t stream);
-
 // "prepare" (state-independent per-chunk quantities into the workspace) and "chain" (the serial
 // state recurrence plus outputs, reading the workspace).  Both return a GDN_* status.
 // with_u = false (for the transposed chain): no U tile; T'' = T diag(beta), bf16 [tiles][64][64], is written at the
@@ -105,11 +110,9 @@ int launch_chain_t(const Problem& p, const Workspace& ws, cudaStream_t stream);
 // Single-launch variant (prepare shared among the four column CTAs of a head, chain in the same kernel);
 // only when all CTAs fit on the GPU at once.
 bool coop_supported(const Problem& p);
-bool coop_dedicated_supported(const Problem& p);
 // skip_prepare (measurement aid): run only the chain roles on a workspace an earlier call left behind.
-// dedicated: 64-column chain CTAs on their own SMs, prepare groups on the remaining SMs.
 int launch_coop(const Problem& p, const Workspace& ws, int* flags, size_t flag_bytes, cudaStream_t stream,
-                bool skip_prepare = false, bool dedicated = false);
+                bool skip_prepare = false);
 
 // Host helper: encode a tiled TMA descriptor for a row-major tensor of `rank` dims
 // (dims/strides innermost first; strides in bytes for dims 1..rank-1).  swizzle_bytes: 128 or 64.

@@ -179,7 +179,7 @@ def gdn_chunk(q, k, v, g, beta, output_final_state=True, initial_state=None, pat
         initial_state: optional [B, Hv, D, D] state to start from (zeros when None).
         path: "auto", or a key of `_lib.PATHS` to force a kernel.
         use_qk_l2norm_in_kernel: L2-normalise every q and k head vector inside the kernels, the switch of the
-            reference's torch definition (reference/gdn_chunk_ref.py:29, :43-45); not on the "fused_*" paths.
+            reference's torch definition (reference/gdn_chunk_ref.py:29, :43-45).
         gate_activations: g and beta are raw projections; the kernels apply g = -softplus(g), beta = sigmoid(beta).
         output_gate: (z, weight) or (z, weight, eps): `out` becomes rmsnorm_gated(out, z, weight), the layer's next
             step (reference: output_gate_interface.py:15-27), applied in place right behind the forward pass.

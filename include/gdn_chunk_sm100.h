@@ -33,8 +33,7 @@ extern "C" {
 /* execution path */
 #define GDN_PATH_AUTO 0          /* DECODE when S <= 8; COOP when S <= 2048 and 4*B*Hv <= #SMs; else TWOPASS_T     */
 #define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
-#define GDN_PATH_FUSED_NV64 2    /* single fused tcgen05 kernel, 64 value columns per CTA            */
-#define GDN_PATH_FUSED_NV32 3    /* single fused tcgen05 kernel, 32 value columns per CTA            */
+                                 /* (values 2, 3 and 10 belonged to kernels that have been removed)    */
 #define GDN_PATH_TWOPASS_NV64 4  /* prepare kernel + chain kernel, 64 value columns per chain CTA    */
 #define GDN_PATH_TWOPASS_NV32 5  /* prepare kernel + chain kernel, 32 value columns per chain CTA    */
 #define GDN_PATH_PREPARE_ONLY 6  /* measurement aid: only the prepare kernel (fills the workspace)    */
@@ -42,8 +41,6 @@ extern "C" {
                                     call with the same arguments and scratch left behind              */
 #define GDN_PATH_COOP 8          /* one launch: the four 32-column CTAs of a head share the prepare work
                                     through the workspace while their chains run; needs 4*B*Hv <= #SMs    */
-#define GDN_PATH_COOP_DEDICATED 10 /* one launch: 64-column chain CTAs (2 per head) on SMs of their own, three
-                                    prepare groups on each remaining SM; needs 8*B*Hv <= 3*#SMs           */
 #define GDN_PATH_COOP_CHAIN_ONLY 9 /* measurement aid: COOP with its prepare roles switched off, on the
                                     workspace an earlier call with the same arguments and scratch left  */
 
@@ -110,8 +107,8 @@ int gdn_chunk_fwd_sm100(const void* q, const void* k, const void* v, const void*
  * reference's CUDA kernels expect normalised inputs and have no such switch, so callers there normalise
  * in a separate pass over q and k.  GDN_FLAG_GATE_ACTIVATIONS: g and beta are the layer's raw gate
  * projections and the kernels apply g = -softplus(g), beta = sigmoid(beta) in fp32 where they load them (no
- * counterpart in the reference, whose callers run these element-wise passes beforehand).  Not available on the GDN_PATH_FUSED_* paths (GDN_ERR_BAD_ARGUMENT);
- * unknown bits are rejected.  flags = 0 is gdn_chunk_fwd_sm100.
+ * counterpart in the reference, whose callers run these element-wise passes beforehand).
+ * Unknown bits are rejected.  flags = 0 is gdn_chunk_fwd_sm100.
  */
 int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const void* g, const void* beta,
                            const float* h0, void* out, float* hT, void* scratch, size_t scratch_bytes,
@@ -215,9 +212,10 @@ const char* gdn_chunk_error_string(int status);
 unsigned long long gdn_chunk_kernel_launches(void);
 
 /*
- * Diagnostic: when `device_buffer` (16 x int64, device memory) is not NULL, CTA (0,0,0) of every
- * later fused-kernel launch writes the SM clock cycles one of its threads spent in each phase of the
- * chunk loop, summed over chunks.  NULL switches it off.  Process-wide, not thread-safe.
+ * Diagnostic, effective only in a library built with -DGDN_DIAGNOSTICS (python -m gdn_qsa_sm80_b200.build
+ * --diagnostics; a production build compiles none of the accounting in): when `device_buffer` (128 x int64,
+ * device memory) is not NULL, one CTA of every later launch writes the SM clock cycles some of its threads
+ * spent in each phase of the chunk loop, summed over chunks.  NULL switches it off.  Process-wide, not thread-safe.
  * Plays the role of the temporary clock64() instrumentation the reference's authors describe
  * (docs/VALIDATION_LOG.md:108-109).
  */

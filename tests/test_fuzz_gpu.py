@@ -22,11 +22,11 @@ def _case(seed):
     B = rnd.randint(1, 5)
     S = rnd.choice([1, 2, 7, 8, 9, 31, 64, 65, 100, 127, 128, 129, 200, 333, 400])
     Hq, Hv = rnd.choice(HEADS)
-    paths = ["auto", "twopass_nv64", "twopass_nv32", "simt"]
+    paths = ["auto", "twopass_nv64", "twopass_nv32", "twopass_t", "simt"]
     if 4 * B * Hv <= 148:
         paths.append("coop")
     if 8 * B * Hv <= 3 * 148:
-        paths.append("coop_dedicated")
+        paths.append("twopass_t")
     if S <= 40:
         paths.append("decode")
     return dict(B=B, S=S, Hq=Hq, Hv=Hv, path=rnd.choice(paths), bf16_gates=rnd.random() < 0.4, h0=rnd.random() < 0.6,

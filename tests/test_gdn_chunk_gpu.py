@@ -19,7 +19,7 @@ from helpers import assert_close, golden, oracle_f32
 
 pytestmark = pytest.mark.gpu
 
-PATHS = ["simt", "fused_nv64", "fused_nv32", "twopass_nv64", "twopass_nv32", "twopass_t", "coop", "coop_dedicated", "decode"]
+PATHS = ["simt", "twopass_nv64", "twopass_nv32", "twopass_t", "coop", "decode"]
 TENSOR_PATHS = PATHS[1:-1]
 
 

@@ -15,7 +15,7 @@ from helpers import assert_close, golden, oracle_f32
 
 pytestmark = pytest.mark.gpu
 
-PATHS = ["simt", "twopass_nv64", "twopass_nv32", "coop", "coop_dedicated", "auto", "decode"]
+PATHS = ["simt", "twopass_nv64", "twopass_nv32", "twopass_t", "coop", "auto", "decode"]
 
 
 def run(q, k, v, g, beta, h0=None, path="auto", l2=True):
@@ -89,13 +89,6 @@ def test_scale_invariance_of_q_and_k():
     b, sb = run(q * 4, k * 8, v, g, beta, path="twopass_nv32")
     assert_close(b, a, "scaled out", rel=1e-3, mabs=5e-3)
     assert_close(sb, sa, "scaled state", rel=1e-3, mabs=5e-3)
-
-
-@pytest.mark.parametrize("path", ["fused_nv64", "fused_nv32"])
-def test_first_generation_fused_paths_reject_the_switch(path):
-    q, k, v, g, beta = raw_inputs(64, seed=1)
-    with pytest.raises(_lib.GdnLibraryError):
-        run(q, k, v, g, beta, path=path)
 
 
 def test_unknown_flag_bits_are_rejected():
