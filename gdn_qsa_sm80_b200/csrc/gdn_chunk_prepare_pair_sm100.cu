@@ -108,13 +108,9 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
     for (; L < num_items && ok; L += gridDim.x) {
         const size_t tile = cur.tile;
-        if (p.gate_act) prep_activate_gates(gv, bv);
-        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, ctx);
-        ctx.sync();
-
         ok = mbar_wait(&bar_tma, ph_tma, p.status, kDevTimeoutTma);
         ph_tma ^= 1;
-        ok = __syncthreads_and(ok);
+        ok = __syncthreads_and(ok);   // also: every warp has left the previous item's accumulator
         if (!ok) break;
 
         if (tid == 0) {   // raw K K^T (lanes 0-63) and Q K^T (lanes 64-127), shared by the two heads
@@ -127,6 +123,10 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             }
             umma_commit(&bar_mma);
         }
+        // the gate cumsum and the decay tables need nothing from the tiles: they run while the product does
+        if (p.gate_act) prep_activate_gates(gv, bv);
+        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, ctx);
+        ctx.sync();
         if (p.l2norm) prep_l2norm_fold(ps, kq, ws.vec + tile * 256, ctx);   // while the UMMAs run
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
