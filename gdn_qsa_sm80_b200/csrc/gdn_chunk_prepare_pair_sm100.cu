@@ -83,6 +83,19 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         tma_load_4d(kq + 24576, &tm_q, &bar_tma, 64, x.hq, x.s0, x.b);
     };
 
+    // optional cycle accounting (diagnostics builds) by thread 0 of CTA 0, summed over its items; slot 15 counts them.
+    // Phases: 0 wait for K/Q, 1 first product + gates, 2 mask epilogue, 3 barrier + bound, 4 inverse, 5 T' / T'',
+    // 6 second product, 7 W staging and stores.
+    const bool prof_on = GDN_DIAG(p.prof != nullptr && tid == 0 && blockIdx.x == 0);
+    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long prof_t = prof_on ? clock64() : 0, prof_n = 0;
+#define GDN_PHASE(n)                                   \
+    if (prof_on) {                                     \
+        const long long now_ = clock64();              \
+        prof_acc[n] += now_ - prof_t;                  \
+        prof_t = now_;                                 \
+    }
+
     long long L = blockIdx.x;
     Item cur = decode(L);
     if (tid == 0) {
@@ -112,6 +125,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         ph_tma ^= 1;
         ok = __syncthreads_and(ok);   // also: every warp has left the previous item's accumulator
         if (!ok) break;
+        GDN_PHASE(0)
 
         if (tid == 0) {   // raw K K^T (lanes 0-63) and Q K^T (lanes 64-127), shared by the two heads
             tc_fence_after_sync();
@@ -135,6 +149,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         if (tid == 0) tma_store_wait_read();
         ok = __syncthreads_and(ok);
         if (!ok) break;
+        GDN_PHASE(1)
         prep_zero_upper_blocks(Tm, ctx);
 
         tc_fence_after_sync();
@@ -195,6 +210,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 }
             }
         }
+        GDN_PHASE(2)
         tc_fence_before_sync();
         ctx.sync();
         if (ws.meta && htid == 0) {
@@ -202,7 +218,9 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             ws.meta[2 * tile + 1] = fmaxf(ps.wsum[0], ps.wsum[1]);
         }
 
+        GDN_PHASE(3)
         prep_invert_unit_lower(As, Tm, Yt, ctx);
+        GDN_PHASE(4)
 
         // both heads are done with their A matrices (the stacked operand lies over head a's) and with the raw
         // products in tensor memory (W goes through the same columns)
@@ -213,6 +231,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             prep_store_scaled_T_row_plain(Tm, ps.bet, i, ws.U + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
         fence_proxy_async_smem();
         __syncthreads();
+        GDN_PHASE(5)
 
         if (tid == 0) {   // W of both heads: [T'_a ; T'_b] K
             tc_fence_after_sync();
@@ -230,6 +249,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         ok = __syncthreads_and(ok);
         if (!ok) break;
         tc_fence_after_sync();
+        GDN_PHASE(6)
 
         // K, Q (the merge temporaries) and the operand are dead: the next item's loads and gate reads start now
         const long long Ln = L + gridDim.x;
@@ -272,7 +292,14 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             }
             tma_store_commit();
         }
+        GDN_PHASE(7)
+        ++prof_n;
         cur = nxt;
+    }
+#undef GDN_PHASE
+    if (prof_on) {
+        for (int n = 0; n < 8; ++n) p.prof[n] = prof_acc[n];
+        p.prof[15] = prof_n;
     }
     if (tid == 0) tma_store_wait_all();
     tc_fence_before_sync();
@@ -292,9 +319,10 @@ int launch_prepare_pair(const Problem& p, const Workspace& ws, cudaStream_t stre
     const long long max_ctas = static_cast<long long>(kPairCtasPerSm) * sm_count();
     const unsigned grid = static_cast<unsigned>(items < max_ctas ? items : max_ctas);
     auto go = [&](auto kernel) -> int {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, QSmem::kDynamic) != cudaSuccess)
+        const uint32_t smem = p.dbg == 4 ? 200 * 1024 : QSmem::kDynamic;   // dbg 4 (experiment): one CTA per SM
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return GDN_ERR_CUDA;
-        kernel<<<grid, 256, QSmem::kDynamic, stream>>>(tq, tk, tw, p, ws, NT, items);
+        kernel<<<grid, 256, smem, stream>>>(tq, tk, tw, p, ws, NT, items);
         count_launch();
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };
