@@ -39,11 +39,13 @@ sys.path.insert(0, ROOT)
 METRIC = "gdn_chunk_fwd_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# dram__bytes_read.sum + dram__bytes_write.sum of one gdn_chain_kernel launch on the default workload (ncu, profiles/)
-CHAIN_DRAM_BYTES_DEFAULT = 361.8e6
-# the same for one gdn_coop_kernel launch: dedicated arrangement (path auto on this workload) / in-CTA arrangement
-COOP_DRAM_BYTES_DEFAULT = 451.2e6
-COOP_IN_CTA_DRAM_BYTES_DEFAULT = 328.7e6
+# dram__bytes_read.sum + dram__bytes_write.sum per step of the dominant kernel, from the ncu captures summarised under
+# profiles/ (workload, kernel) -> bytes; anything not listed is reported as null
+DRAM_TRAFFIC = {
+    ("default", "gdn_chain_t_kernel"): 367.7e6,      # launch 1 (segments) 329.0 MB + launch 2 (first chunks again) 38.7 MB
+    ("default", "gdn_chain_kernel"): 361.8e6,
+    ("default", "gdn_coop_kernel"): 328.7e6,
+}
 
 
 def flops_per_token(Hq, Hv, C=64, D=128):
@@ -777,14 +779,15 @@ def main():
              "hbm": {"achieved": by / step_s / 1e9, "frac": by / step_s / 1e9 / peaks["hbm_gbs"],
                      "algorithmic_bytes_per_step": by, "peak": peaks["hbm_gbs"], "unit": "GB/s"}}
     if per_kernel:
-        # flops of the chain kernel: W S, Q S, K^T v~ (2 D D each) and P v_new (2 C D) per value head and token;
-        # the prepare kernel has the rest (K K^T, Q K^T per qk head; T K, T V per value head)
-        fl_chain = w.Hv * (6 * 128 * 128 + 2 * 64 * 128) * tokens_local
+        # flops of the chain kernel: W S, Q S, K^T v~ (2 D D each) and P v_new (2 C D) per value head and token - the
+        # transposed chain also forms U = T'' V (2 C D); the prepare kernel has the rest (K K^T, Q K^T per qk head;
+        # T K, and T V where the chain does not do it, per value head)
+        fl_chain = w.Hv * (6 * 128 * 128 + (4 if transposed else 2) * 64 * 128) * tokens_local
         fl_prep = fl - fl_chain
         k_s = per_kernel["chain_only"] * 1e-3
         tf = fl_chain / k_s / 1e12
         # DRAM bytes of one chain launch on the default workload, from an ncu capture (profiles/): read + write
-        traffic = CHAIN_DRAM_BYTES_DEFAULT if (args.workload == "default" and world == 1 and not transposed) else None
+        traffic = DRAM_TRAFFIC.get((args.workload, "gdn_chain_t_kernel" if transposed else "gdn_chain_kernel")) if world == 1 else None
         roofline = {"kernel": "gdn_chain_t_kernel" if transposed else "gdn_chain_kernel", "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"],
                     "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "traffic": traffic,
                     "peak_kind": f"{peak_kind} (burst cuBLAS bf16)", "algorithmic_flops_per_launch": fl_chain,
@@ -796,9 +799,7 @@ def main():
                     "whole_step": whole}
     elif single_launch:
         # one kernel per step: its duration is the step's (CUDA events around the launch)
-        traffic = None
-        if args.workload == "default" and world == 1:
-            traffic = COOP_IN_CTA_DRAM_BYTES_DEFAULT if args.path == "coop" else COOP_DRAM_BYTES_DEFAULT
+        traffic = DRAM_TRAFFIC.get((args.workload, "gdn_coop_kernel")) if world == 1 else None
         roofline = {"kernel": "gdn_coop_kernel", "bound": "tensor", "achieved": whole["achieved"], "peak": peaks["bf16_tflops"],
                     "unit": "TFLOP/s", "frac": whole["frac"], "traffic": traffic,
                     "peak_kind": f"{peak_kind} (burst cuBLAS bf16)", "algorithmic_flops_per_launch": fl,
