@@ -315,7 +315,7 @@ const char* gdn_chunk_error_string(int status) {
 // Some hosts of this library may not allocate device memory at all when they call it: a serving
 // runtime that reserved its whole memory budget at start-up and hands out fixed buffers for inputs
 // and outputs only, or a latency-critical loop in which cudaMalloc (which synchronises the whole
-// device) must never run.  For them the workspace of the prepare + chain path lives in the array
+// device) must never run.  For them the workspace of the automatic path (whichever kernels it picks) lives in the array
 // below, which every GPU that loads this library holds until the process exits.
 //
 // `g_noalloc_scratch` is a HOST-side handle in host code, not a device address; its device address
