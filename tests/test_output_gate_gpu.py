@@ -55,7 +55,7 @@ def test_leading_shape_eps_and_errors():
         rmsnorm_gated(y.cpu(), z.cpu(), w.cpu())
 
 
-@pytest.mark.parametrize("path", ["auto", "twopass_nv64", "simt"])
+@pytest.mark.parametrize("path", ["auto", "twopass_nv64", "twopass_t", "simt"])
 @pytest.mark.parametrize("S", [100, 1024])
 def test_chained_behind_the_forward_pass(path, S):
     q, k, v, g, beta, _ = make_inputs("default", seed=S, B=2, S=S, Hq=2, Hv=4)
@@ -73,3 +73,23 @@ def test_chained_behind_the_forward_pass(path, S):
     # same bits as the two separate calls
     o2, _ = gdn_chunk(q.to(dev), k.to(dev), v.to(dev), g.to(dev), beta.to(dev), path=path)
     assert torch.equal(rmsnorm_gated(o2, z.to(dev), w.to(dev)), out)
+
+
+def test_behind_the_transposed_chain_with_split_sequences():
+    """Long sequences, few heads: the transposed chain splits them on the device (two launches that both write
+    outputs); the gate behind them gives the same bits as the forward pass followed by the separate call."""
+    S = 4096
+    q, k, v, g, beta, h0 = make_inputs("default", seed=31, B=1, S=S, Hq=4, Hv=8)
+    gen = torch.Generator().manual_seed(32)
+    z = (1.5 * torch.randn(1, S, 8, 128, generator=gen)).bfloat16()
+    w = (1 + 0.1 * torch.randn(128, generator=gen)).bfloat16()
+    dev = "cuda"
+    d = [t.to(dev) for t in (q, k, v, g, beta)]
+    out, st = gdn_chunk(*d, initial_state=h0.to(dev), output_gate=(z, w))
+    check_device_status()
+    o2, s2 = gdn_chunk(*d, initial_state=h0.to(dev))
+    assert torch.equal(rmsnorm_gated(o2, z.to(dev), w.to(dev)), out) and torch.equal(st, s2)
+    ref_o, _ = oracle_f32(q, k, v, g, beta, h0)
+    ref = O.rmsnorm_gated(ref_o, z.float().numpy(), w.float().numpy())
+    # outputs are on the scale of silu(z) (up to ~6 here) with bf16 rounding: the relative bound is the meaningful one
+    assert_close(out.float().cpu().numpy(), ref, "gated out", mabs=2.5e-1)
