@@ -109,9 +109,10 @@ __device__ __forceinline__ bool wait_tile_flag(const int* flag, int* status, vol
 }
 
 // The stretch of chunks [t0, t1) of one (batch, value head) a CTA runs, the state it starts from (a 128 x 128 fp32
-// matrix, [dk][dv]; null = zeros) and where the state it ends with goes (null = nowhere).
+// matrix, [dk][dv]; null = zeros) and where the state it ends with goes (null = nowhere).  Outputs are stored from
+// chunk t_store on: chunks [t0, t_store) only bring the state up to date (the warm-up of a segment).
 struct Span {
-    int t0, t1;
+    int t0, t1, t_store;
     const float* s_in;
     float* s_out;
 };
@@ -296,7 +297,8 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
             GDN_OPHASE(1)
             GDN_TL(58 + warp - 8)
             __nv_bfloat16* dst = p.out + ((static_cast<size_t>(b) * p.S + t * kChunk) * p.Hv + hv) * kD + dv;
-            const int valid = min(kChunk, p.S - t * kChunk);
+            const size_t row_stride = static_cast<size_t>(p.Hv) * kD;
+            const int valid = t >= sp.t_store ? min(kChunk, p.S - t * kChunk) : 0;   // warm-up chunks store nothing
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
                 uint32_t c[32];
@@ -308,32 +310,25 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
                     if (lane == 0) mbar_arrive_a(cb(B_PVDONE));
                     GDN_TL(62 + warp - 8)
                 }
-                if (p.dbg == 1) {          // experiment: no stores
-                    float acc = 0.f;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) acc += __uint_as_float(o[32 * h2 + j]) + __uint_as_float(c[j]);
-                    if (acc == 1234.5f) dst[0] = __float2bfloat16(acc);
-                } else if (p.dbg == 2) {   // experiment: lane pairs exchange values, 4-byte stores
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const float x0 = fmaf(-qf[32 * h2 + j], __uint_as_float(o[32 * h2 + j]), __uint_as_float(c[j]));
-                        const float x1 = fmaf(-qf[32 * h2 + j + 1], __uint_as_float(o[32 * h2 + j + 1]), __uint_as_float(c[j + 1]));
-                        const float recv = __shfl_xor_sync(0xffffffffu, (lane & 1) ? x0 : x1, 1);
-                        const int tok = 32 * h2 + j + (lane & 1);
-                        const uint32_t pk = (lane & 1) ? pack_bf16x2(recv, x1) : pack_bf16x2(x0, recv);
-                        if (tok < valid)
-                            *reinterpret_cast<uint32_t*>(dst - (lane & 1) + static_cast<size_t>(tok) * p.Hv * kD) = pk;
-                    }
-                } else {
+                // O^T[dv][j] = scale e^gamma_j (S^T Q^T) + v_new^T P^T: a warp stores 64 contiguous bytes of row j
+                __nv_bfloat16* drow = dst + static_cast<size_t>(32 * h2) * row_stride;
+                if (valid == kChunk) {          // whole chunk (the common case): no per-row test
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         const float4 f = *reinterpret_cast<const float4*>(qf + 32 * h2 + j);
                         const float fq[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            if (32 * h2 + j + u < valid)
-                                dst[static_cast<size_t>(32 * h2 + j + u) * p.Hv * kD] =
-                                    __float2bfloat16(fmaf(-fq[u], __uint_as_float(o[32 * h2 + j + u]), __uint_as_float(c[j + u])));
+                        for (int u = 0; u < 4; ++u) {
+                            *drow = __float2bfloat16(fmaf(-fq[u], __uint_as_float(o[32 * h2 + j + u]), __uint_as_float(c[j + u])));
+                            drow += row_stride;
+                        }
+                    }
+                } else if (valid > 32 * h2) {   // ragged tail
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (32 * h2 + j < valid)
+                            *drow = __float2bfloat16(fmaf(-qf[32 * h2 + j], __uint_as_float(o[32 * h2 + j]), __uint_as_float(c[j])));
+                        drow += row_stride;
                     }
                 }
             }

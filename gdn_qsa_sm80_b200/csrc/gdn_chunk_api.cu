@@ -128,19 +128,18 @@ static bool path_uses_workspace(int path) {
            path == GDN_PATH_PREPARE_ONLY_T || path == GDN_PATH_CHAIN_ONLY_T;
 }
 
-// segment states the path keeps behind the tile arrays (only the transposed chain splits sequences)
-static size_t seg_states_of(int B, int S, int Hv, int path) {
+// segments the path cuts every sequence into (only the transposed chain splits sequences; 1 = not split)
+static int segments_of(int B, int S, int Hv, int path) {
     if (path != GDN_PATH_TWOPASS_T && path != GDN_PATH_AUTO && path != GDN_PATH_PREPARE_ONLY_T && path != GDN_PATH_CHAIN_ONLY_T)
-        return 0;
-    const int g = chain_segments(B, Hv, S, sm_count());
-    return g > 1 ? static_cast<size_t>(B) * Hv * g : 0;
+        return 1;
+    return chain_segments(B, Hv, S, sm_count());
 }
 
 size_t gdn_chunk_scratch_bytes(int B, int S, int Hq, int Hv, int path) {
     (void)Hq;
     if (B <= 0 || S < 0 || Hv <= 0) return 0;
     if (!path_uses_workspace(path)) return 256;   // only the device status word, padded
-    return workspace_layout(tiles_of(B, S, Hv), seg_states_of(B, S, Hv, path)).total;
+    return workspace_layout(tiles_of(B, S, Hv), segments_of(B, S, Hv, path) > 1).total;
 }
 
 int gdn_chunk_workspace_offsets(int B, int S, int Hq, int Hv, size_t* offsets) {
@@ -249,21 +248,20 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     int nv;
     if (path == GDN_PATH_TWOPASS_NV32) nv = 32;
     else nv = 64;
-    // the transposed chain splits sequences when the scratch buffer has room for the segment states (a caller that
-    // sized it for an unsplit run, like the fixed-array entry point, gets the unsplit run)
+    // the transposed chain splits sequences when the scratch buffer has room for the per-tile scalars its decision
+    // reads (a caller that sized it for an unsplit run, like the fixed-array entry point, gets the unsplit run)
     const bool transposed = path == GDN_PATH_TWOPASS_T || path == GDN_PATH_PREPARE_ONLY_T || path == GDN_PATH_CHAIN_ONLY_T;
-    size_t seg_states = transposed ? seg_states_of(B, S, Hv, path) : 0;
-    if (seg_states && scratch_bytes < workspace_layout(tiles_of(B, S, Hv), seg_states).total) seg_states = 0;
-    const WorkspaceLayout l = workspace_layout(tiles_of(B, S, Hv), seg_states);
+    int n_seg = transposed ? segments_of(B, S, Hv, path) : 1;
+    if (n_seg > 1 && scratch_bytes < workspace_layout(tiles_of(B, S, Hv), true).total) n_seg = 1;
+    const WorkspaceLayout l = workspace_layout(tiles_of(B, S, Hv), n_seg > 1);
     uint8_t* base = static_cast<uint8_t*>(scratch);
     Workspace ws;
     ws.W = reinterpret_cast<__nv_bfloat16*>(base + l.W);
     ws.P = reinterpret_cast<__nv_bfloat16*>(base + l.P);
     ws.U = reinterpret_cast<__nv_bfloat16*>(base + l.U);
     ws.vec = reinterpret_cast<float*>(base + l.vec);
-    ws.meta = seg_states ? reinterpret_cast<float*>(base + l.meta) : nullptr;
-    ws.seg_state = seg_states ? reinterpret_cast<float*>(base + l.seg_state) : nullptr;
-    ws.n_seg = seg_states ? static_cast<int>(seg_states / (static_cast<size_t>(B) * Hv)) : 1;
+    ws.meta = n_seg > 1 ? reinterpret_cast<float*>(base + l.meta) : nullptr;
+    ws.n_seg = n_seg;
     if (path == GDN_PATH_COOP_CHAIN_ONLY)
         return then_gate(launch_coop(p, ws, reinterpret_cast<int*>(base + l.flags), l.flag_bytes, stream, true));
     if (path == GDN_PATH_COOP) {

@@ -4,19 +4,21 @@
 // launcher.  Stands in for the reference's gdn_recurrence_kernel (csrc/gdn_chunk/gdn_kernel.cu:1027-1271).
 //
 // Split sequences (ws.n_seg = G > 1, chosen from the shape when there are too few sequences to fill the GPU): every
-// sequence is cut into G segments of L chunks.  The second level of the reference's scan has the same purpose
-// (csrc/gdn_chunk/gdn_ops.cu:1002-1012, gdn_scan_stage1.cu:7-18); here it rests on an exact bound instead of a
-// propagated transfer matrix.  A segment maps its incoming state by S_out = A S_in + B with
-// A = prod_t exp(g_t)(I - beta_t k_t k_t^T), and |I - beta k k^T|_2 <= 1 whenever 0 <= beta |k|^2 <= 2, so
-// |A|_2 <= exp(sum of g).  Once that sum, taken from the segment's first token, is below -115 (exp(-115) < 2^-149),
-// the incoming state no longer shows in fp32: every later output of the segment and its final state are the same
-// from a zero state.  Per head, on the device, from the per-chunk sums the prepare kernel left (ws.meta):
-//   * if every segment after the first forgets its incoming state within its own length (after p_s chunks) and the
-//     premise on beta |k|^2 holds:  launch 1 runs all G segments at once from zero states (segment 0 from the
-//     caller's initial state) and keeps every segment's final state; launch 2 recomputes chunks [0, p_s) of every
-//     segment s >= 1 from the final state of segment s-1 and overwrites those outputs;
+// sequence is cut into G segments of L chunks that run as independent CTAs of ONE launch.  The second level of the
+// reference's scan has the same purpose (csrc/gdn_chunk/gdn_ops.cu:1002-1012, gdn_scan_stage1.cu:7-18); here it rests
+// on an exact bound instead of a propagated transfer matrix.  A stretch of tokens maps its incoming state by
+// S_out = A S_in + B with A = prod_t exp(g_t)(I - beta_t k_t k_t^T), and |I - beta k k^T|_2 <= 1 whenever
+// 0 <= beta |k|^2 <= 2, so |A|_2 <= exp(sum of g).  Once that sum is below -115 (exp(-115) < 2^-149) the incoming
+// state no longer shows in fp32: the state after the stretch is the same from a zero state.  So segment s >= 1
+// starts from a ZERO state p_s chunks before its first chunk, where p_s is the shortest stretch ending at the segment
+// boundary whose sum of g is below -115 ("warm-up": its outputs are not stored), and from its first chunk on its
+// state, its outputs and its final state are those of the serial run.  Per head, on the device, from the per-chunk
+// scalars the prepare kernel left (ws.meta):
+//   * if every segment s >= 1 has such a warm-up no longer than a segment and the premise on beta |k|^2 holds on
+//     every chunk, the G CTAs of the head run their segments at once (segment 0 from the caller's initial state, the
+//     last one writes the final state);
 //   * otherwise the CTA of segment 0 runs the whole sequence serially and the others return at once.
-// No host read, no data-dependent launch; results equal the serial chain's in either case.
+// No host read, no data-dependent launch, no state passed between CTAs; results equal the serial chain's.
 #include <cuda.h>
 
 #include "../../include/gdn_chunk_sm100.h"
@@ -29,39 +31,43 @@ namespace {
 
 constexpr int kMaxSeg = 8;
 
-// One warp of a CTA: can this head be run as independent segments, and after how many chunks has segment s forgotten
-// its incoming state (horizon[s], 1 <= s < G)?  meta: [NT][2] of this head.
-__device__ __forceinline__ bool head_is_splittable(const float* meta, int NT, int G, int L, int lane, int* horizon) {
+// One warp of a CTA: can this head be run as independent segments, and how many chunks of warm-up does segment s
+// need (warm[s], 1 <= s < G)?  meta: [NT][2] of this head.
+__device__ __forceinline__ bool head_is_splittable(const float* meta, int NT, int G, int L, int lane, int* warm) {
     float bmax = 0.f;
     for (int t = lane; t < NT; t += 32) bmax = fmaxf(bmax, meta[2 * t + 1]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
     bool ok = bmax <= 2.f;            // false for NaN and for the +inf that marks a gate out of range
     for (int s = 1; s < G; ++s) {
-        const int t0 = s * L, t1 = min(NT, t0 + L);
+        const int t0 = s * L;         // t0 >= L: at least L chunks lie before the boundary
+        if (t0 >= NT) {
+            if (lane == 0) warm[s] = 0;
+            continue;
+        }
         int p = 0;
         float carry = 0.f;
-        for (int base = t0; base < t1 && p == 0; base += 32) {
-            const int t = base + lane;
-            float x = t < t1 ? meta[2 * t] : 0.f;
+        for (int base = 0; base < L && p == 0; base += 32) {     // backwards from chunk t0 - 1, at most L chunks
+            const int d = base + lane;
+            float x = d < L ? meta[2 * (t0 - 1 - d)] : 0.f;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const float y = __shfl_up_sync(0xffffffffu, x, o);
                 if (lane >= o) x += y;
             }
             x += carry;
-            const unsigned below = __ballot_sync(0xffffffffu, t < t1 && x < kForgetLn);
-            if (below) p = base - t0 + __ffs(below);      // chunks [0, p) carry the incoming state
+            const unsigned below = __ballot_sync(0xffffffffu, d < L && x < kForgetLn);
+            if (below) p = base + __ffs(below);                  // chunks [t0 - p, t0) make the state forget
             carry = __shfl_sync(0xffffffffu, x, 31);
         }
-        if (t0 < NT && p == 0) ok = false;                // this segment never forgets: no split for this head
-        if (lane == 0) horizon[s] = p;
+        if (p == 0) ok = false;                                  // no warm-up within a segment's length: no split
+        if (lane == 0) warm[s] = p;
     }
     return ok;
 }
 
-// PASS 0: sequences are not split.  PASS 1 / 2: the two launches of a split run (blockIdx.z = segment, resp. segment - 1).
-template <int PASS>
+// SPLIT = false: one CTA per sequence.  SPLIT = true: blockIdx.z = segment.
+template <bool SPLIT>
 __global__ void __launch_bounds__(chain_t::kThreads, 1)
 gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
@@ -75,7 +81,7 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ int split_ok;
-    __shared__ int horizon[kMaxSeg];
+    __shared__ int warm[kMaxSeg];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hv = blockIdx.x, b = blockIdx.y;
@@ -92,8 +98,8 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_alloc(&tmem_slot, chain_t::kTmemCols);
         tmem_relinquish();
     }
-    if (PASS != 0 && warp == 1) {
-        const bool ok = head_is_splittable(ws.meta + seq * NT * 2, NT, ws.n_seg, L, lane, horizon);
+    if (SPLIT && warp == 1) {
+        const bool ok = head_is_splittable(ws.meta + seq * NT * 2, NT, ws.n_seg, L, lane, warm);
         if (lane == 0) split_ok = ok ? 1 : 0;
     }
     chain_t::init_zero_blocks(sm, tid, chain_t::kThreads);
@@ -106,22 +112,17 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
     const float* h0 = p.h0 ? p.h0 + seq * kD * kD : nullptr;
     float* hT = p.hT ? p.hT + seq * kD * kD : nullptr;
-    chain_t::Span sp{0, 0, nullptr, nullptr};
-    if (PASS == 0) {
-        sp = chain_t::Span{0, NT, h0, hT};
+    chain_t::Span sp{0, 0, 0, nullptr, nullptr};
+    if (!SPLIT) {
+        sp = chain_t::Span{0, NT, 0, h0, hT};
     } else {
-        const int G = ws.n_seg;
-        float* seg_states = ws.seg_state + seq * G * kD * kD;
-        const int seg = PASS == 1 ? static_cast<int>(blockIdx.z) : static_cast<int>(blockIdx.z) + 1;
+        const int seg = static_cast<int>(blockIdx.z);
         const int t0 = seg * L, t1 = min(NT, t0 + L);
-        if (PASS == 1) {
-            if (!split_ok) {
-                if (seg == 0) sp = chain_t::Span{0, NT, h0, hT};
-            } else if (t0 < NT) {
-                sp = chain_t::Span{t0, t1, seg == 0 ? h0 : nullptr, t1 == NT ? hT : seg_states + static_cast<size_t>(seg) * kD * kD};
-            }
-        } else if (split_ok && t0 < NT) {
-            sp = chain_t::Span{t0, min(t1, t0 + horizon[seg]), seg_states + static_cast<size_t>(seg - 1) * kD * kD, nullptr};
+        if (!split_ok) {
+            if (seg == 0) sp = chain_t::Span{0, NT, 0, h0, hT};
+        } else if (t0 < NT) {
+            if (seg == 0) sp = chain_t::Span{0, t1, 0, h0, t1 == NT ? hT : nullptr};
+            else sp = chain_t::Span{t0 - warm[seg], t1, t0, nullptr, t1 == NT ? hT : nullptr};
         }
     }
     if (sp.t0 < sp.t1)
@@ -159,11 +160,8 @@ int launch_chain_t(const Problem& p, const Workspace& ws, cudaStream_t stream) {
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };
     const int G = ws.n_seg;
-    if (G <= 1 || G > kMaxSeg || !ws.meta || !ws.seg_state) return go(gdn_chain_t_kernel<0>, 1, NT);
-    const int L = (NT + G - 1) / G;
-    const int st = go(gdn_chain_t_kernel<1>, static_cast<unsigned>(G), L);
-    if (st != GDN_OK) return st;
-    return go(gdn_chain_t_kernel<2>, static_cast<unsigned>(G - 1), L);
+    if (G <= 1 || G > kMaxSeg || !ws.meta) return go(gdn_chain_t_kernel<false>, 1, NT);
+    return go(gdn_chain_t_kernel<true>, static_cast<unsigned>(G), (NT + G - 1) / G);
 }
 
 }  // namespace gdn

@@ -46,17 +46,17 @@ struct Workspace {
     __nv_bfloat16* P;   // [tiles][64][64]   masked, scaled Q K^T
     __nv_bfloat16* U;   // [tiles][64][128]  U = T (beta V); the transposed chain's T'' = T diag(beta), [tiles][64][64], instead
     float* vec;         // [tiles][256]      exp(gamma_C-gamma_i) | scale exp(gamma_i) | exp(gamma_C) | pad
-    float* meta;        // [tiles][2]        sum of g over the chunk | max_j beta_j |k_j|^2 (+inf if a gate is out of range)
-    float* seg_state;   // [B*Hv][n_seg][128][128] fp32: state every segment of a split sequence ends with (may be null)
+    float* meta;        // [tiles][2]        sum of g over the chunk | max_j beta_j |k_j|^2 (+inf if a gate is out of range);
+                        //                   null when sequences are not split
     int n_seg;          // segments a sequence is split into by the transposed chain (1 = not split)
 };
 
 // Byte offsets of the workspace arrays inside the scratch buffer (the status word sits at offset 0).
 struct WorkspaceLayout {
-    size_t W, P, U, vec, flags, flag_bytes, meta, seg_state, total;
+    size_t W, P, U, vec, flags, flag_bytes, meta, total;
 };
-// seg_states: number of 128 x 128 fp32 segment states kept behind the tile arrays (0 when sequences are not split)
-inline WorkspaceLayout workspace_layout(size_t tiles, size_t seg_states = 0) {
+// with_meta: room for the two scalars per tile that the on-device decision to split sequences reads
+inline WorkspaceLayout workspace_layout(size_t tiles, bool with_meta = false) {
     WorkspaceLayout l;
     l.W = 1024;
     l.P = l.W + tiles * 16384;
@@ -65,8 +65,7 @@ inline WorkspaceLayout workspace_layout(size_t tiles, size_t seg_states = 0) {
     l.flags = l.vec + tiles * 1024;                      // one int per tile: "prepared" flags of the single-launch path
     l.flag_bytes = (tiles * 4 + 1023) / 1024 * 1024;
     l.meta = l.flags + l.flag_bytes;
-    l.seg_state = l.meta + (seg_states ? (tiles * 8 + 1023) / 1024 * 1024 : 0);
-    l.total = l.seg_state + seg_states * 65536;
+    l.total = l.meta + (with_meta ? (tiles * 8 + 1023) / 1024 * 1024 : 0);
     return l;
 }
 // Into how many contiguous segments the transposed chain splits every sequence (1 = not at all): only when there are
@@ -102,10 +101,9 @@ int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream, b
 int launch_prepare_pair(const Problem& p, const Workspace& ws, cudaStream_t stream);
 int launch_chain(const Problem& p, const Workspace& ws, int nv, cudaStream_t stream);
 // The chain in transposed form: one CTA per (batch, value head), all 128 value columns (gdn_chain_t_device.cuh).
-// With ws.n_seg > 1 every sequence is cut into ws.n_seg segments that run as independent chains from a zero state,
-// followed by a second launch that recomputes the first chunks of every segment from the state the segment before
-// it ended with - for the heads whose gates make every segment forget its incoming state (decided on the device
-// from ws.meta); the other heads run as one serial chain.  Exact in both cases.
+// With ws.n_seg > 1 every sequence is cut into ws.n_seg segments that run as independent chains of one launch, each
+// warmed up from a zero state over the chunks before it that make the state forget its past - for the heads whose
+// gates allow that (decided on the device from ws.meta); the other heads run as one serial chain.  Exact in both cases.
 int launch_chain_t(const Problem& p, const Workspace& ws, cudaStream_t stream);
 // Single-launch variant (prepare shared among the four column CTAs of a head, chain in the same kernel);
 // only when all CTAs fit on the GPU at once.
