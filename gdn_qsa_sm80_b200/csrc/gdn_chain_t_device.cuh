@@ -5,16 +5,14 @@
 // the state, v_new and its decay-scaled copy) are A operands, which tcgen05.mma may read from tensor memory, and
 // the B operands are tiles exactly as TMA loaded them.  With S^T the [dv x dk] state (thread = one dv row, fp32
 // registers), per 64-token chunk (notation of gdn_qsa_sm80/reference/gdn_chunk_ref.py:90-94):
-//   E0   ACC_VQ  = V^T [T'';0]^T        (A = the raw V tile read MN-major, B = T'' = T diag(beta) as prepared, over a
-//                                        block of zeros: columns 0-63 become U^T = (T'' V)^T, columns 64-127 zero)
-//   E1   ACC_VQ -= S^T [W;Q]^T          (A = bf16 S^T in TMEM, negated; B = the W and Q tiles as loaded, stacked)
-//        columns 0-63: v_new^T = U^T - S^T W^T (ref :91);  columns 64-127: -(S^T Q^T)
+//   E0   ACC_V   = V^T T''^T            (A = the raw V tile read MN-major, B = T'' = T diag(beta) as prepared) = U^T
+//   E1   ACC_V  -= S^T W^T              (A = bf16 S^T in TMEM, negated; B = the W tile as loaded) -> v_new^T   (ref :91)
+//   E1'  ACC_QS  = S^T Q^T              (same A, not negated; B = the Q tile; nothing on the critical path waits for it)
 //   E2   ACC_S  = v~^T K                (A = bf16 v~^T in TMEM, B = K as loaded, MN-major)
 //        S^T <- exp(gamma_C) S^T + ACC_S                                                                   (ref :94)
 //   E3   ACC_PV = v_new^T P^T           (A = bf16 v_new^T in TMEM, B = P as loaded)
 //        O^T = scale exp(gamma_i) (S^T Q^T) + ACC_PV  (column factors)                                   (ref :92-93)
-// One UMMA instruction costs about the same tensor-pipe time for 64 as for 128 columns (measured), hence the
-// stacked 128-column products: 20 instructions per chunk.
+// 28 UMMA instructions per chunk, of which the 8 of E1 and the 4 of E2 are on the critical path.
 // Nothing the recurrence produces is written to shared memory, no generic-to-async proxy fence sits on the critical
 // path, and one CTA carries all 128 value columns of a head, so every workspace tile is read once per head.
 // The reference keeps its state in registers for the same reason (csrc/gdn_chunk/gdn_kernel.cu:1581-1606).
@@ -37,16 +35,15 @@ constexpr int kVecSlots = 4;
 constexpr int kThreads = 14 * 32;
 // one stage of the ring (every tile 1024-byte aligned; two 64-column halves of 64 rows x 128 B each)
 // [W;Q]: two dk-halves of 128 rows x 128 B, rows 0-63 W, rows 64-127 Q
-// T2: T'' (64 rows x 128 B) directly followed by ZR, 8 KB of zeros written once: together the 128-row operand [T'';0]
-constexpr uint32_t KT = 0, WQ = 16384, VT = 49152, PT = 65536, T2 = 73728, ZR = 81920, kStage = 90112;
-constexpr uint32_t kStageTx = kStage - 8192 + 1024;       // the stage's tiles (not the zeros) plus its slot of per-token factors
+constexpr uint32_t KT = 0, WQ = 16384, VT = 49152, PT = 65536, T2 = 73728, kStage = 81920;
+constexpr uint32_t kStageTx = kStage + 1024;              // the stage plus its slot of per-token factors
 constexpr uint32_t VEC = kStages * kStage;                // kVecSlots x 256 floats
 constexpr uint32_t kBytes = VEC + kVecSlots * 1024;
-static_assert(kStage % 1024 == 0 && ZR == T2 + 8192, "tiles must stay 1024-byte aligned; the zeros follow T''");
+static_assert(kStage % 1024 == 0, "tiles must stay 1024-byte aligned");
 
 // tensor-memory columns (32-bit) of one chain CTA
 constexpr uint32_t ACC_S = 0;      // 128: v~^T K
-constexpr uint32_t ACC_VQ = 128;   // 128: v_new^T (64) | -(S^T Q^T) (64)
+constexpr uint32_t ACC_VQ = 128;   // 128: v_new^T (64) | S^T Q^T (64)
 constexpr uint32_t ACC_PV = 256;   // 64: v_new^T P^T
 constexpr uint32_t A_S = 320;      // 64: bf16 S^T (128 dk)
 constexpr uint32_t A_VN = 384;     // 32: bf16 v_new^T (64 tokens)
@@ -57,7 +54,7 @@ constexpr int kTimeoutFull = 0x401, kTimeoutEmpty = 0x402, kTimeoutV = 0x403, kT
               kTimeoutState = 0x406, kTimeoutO = 0x407, kTimeoutQsDone = 0x408, kTimeoutFlag = 0x409, kTimeoutPvDone = 0x40a;
 
 // The CTA's barriers: kNumBars consecutive 8-byte mbarriers in shared memory, addressed by their shared-window address.
-enum : uint32_t { B_FULL = 0, B_EMPTY = kStages, B_V = 2 * kStages, B_VN, B_S, B_STATE, B_O, B_QSDONE, B_PVDONE, kNumBars };
+enum : uint32_t { B_FULL = 0, B_EMPTY = kStages, B_V = 2 * kStages, B_Q, B_VN, B_S, B_STATE, B_O, B_QSDONE, B_PVDONE, kNumBars };
 struct Bars {
     uint32_t base;                     // shared-window address of barrier 0
     __device__ __forceinline__ uint32_t operator()(uint32_t i) const { return base + 8u * i; }
@@ -69,20 +66,13 @@ __device__ __forceinline__ void init_bars(uint64_t* bars) {   // one thread
         mbar_init(&bars[B_EMPTY + s], 5);   // the commit behind the chunk's last UMMA + the four output warps (see there)
     }
     mbar_init(&bars[B_V], 1);
+    mbar_init(&bars[B_Q], 1);
     mbar_init(&bars[B_VN], 8);
     mbar_init(&bars[B_S], 1);
     mbar_init(&bars[B_STATE], 8);
     mbar_init(&bars[B_O], 1);
     mbar_init(&bars[B_QSDONE], 4);
     mbar_init(&bars[B_PVDONE], 4);
-}
-
-// The blocks of zeros behind every stage's T'' tile (all threads of the CTA; followed by a proxy fence and a CTA
-// barrier in the caller).
-__device__ __forceinline__ void init_zero_blocks(uint8_t* sm, int tid, int nthreads) {
-    for (int s = 0; s < kStages; ++s)
-        for (uint32_t e = tid * 16; e < 8192; e += nthreads * 16)
-            *reinterpret_cast<uint4*>(sm + s * kStage + ZR + e) = make_uint4(0, 0, 0, 0);
 }
 
 __device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
@@ -170,8 +160,8 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
     if (warp == 13) {
         if (lane != 0) return;
         // ------------------------------- UMMA issuer --------------------------------------------------------------
-        constexpr uint32_t idesc_e0 = umma_idesc_bf16(128, 128, MAJOR_MN, MAJOR_K);
-        constexpr uint32_t idesc_e1 = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_K, 1);    // negated A
+        constexpr uint32_t idesc_e0 = umma_idesc_bf16(128, 64, MAJOR_MN, MAJOR_K);
+        constexpr uint32_t idesc_e1 = umma_idesc_bf16(128, 64, MAJOR_K, MAJOR_K, 1);    // negated A
         constexpr uint32_t idesc_e2 = umma_idesc_bf16(128, 128, MAJOR_K, MAJOR_MN);
         constexpr uint32_t idesc_e3 = umma_idesc_bf16(128, 64, MAJOR_K, MAJOR_K);
         const bool prof = GDN_DIAG(p.prof != nullptr && prof_cta);
@@ -193,7 +183,7 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
             tc_fence_after_sync();
             GDN_TPHASE(0)
             GDN_TL(1)
-            {   // E0: ACC_VQ = V^T [T'';0]^T
+            {   // E0: ACC_V = V^T T''^T
                 const uint64_t a0 = umma_smem_desc(sb + VT, 8192, 1024, SWZ_128B);
                 const uint64_t b0 = umma_smem_desc(sb + T2, 16, 1024, SWZ_128B);
 #pragma unroll
@@ -206,12 +196,16 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
             tc_fence_after_sync();
             GDN_TPHASE(2)
             GDN_TL(3)
-            {   // E1: ACC_VQ -= S^T [W;Q]^T
+            {   // E1: ACC_V -= S^T W^T (the critical one), then E1': ACC_QS = S^T Q^T
                 const uint64_t w0 = umma_smem_desc(sb + WQ, 16, 1024, SWZ_128B);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     umma_bf16_ts(tmem + ACC_VQ, tmem + A_S + ks * 8, w0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), idesc_e1, 1);
                 umma_commit_a(cb(B_V));
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    umma_bf16_ts(tmem + ACC_VQ + 64, tmem + A_S + ks * 8, w0 + (((ks >> 2) * 16384 + 8192 + (ks & 3) * 32) >> 4), idesc_e3, ks > 0);
+                umma_commit_a(cb(B_Q));
             }
             GDN_TPHASE(3)
             GDN_TL(4)
@@ -273,13 +267,13 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
             bool ok = mbar_wait_abortable_a(cb(B_FULL + s), (n / kStages) & 1, p.status, kTimeoutFull, abortp);
             __syncwarp();
             if (lane == 0) mbar_arrive_a(cb(B_EMPTY + s));
-            ok = mbar_wait_abortable_a(cb(B_V), n & 1, p.status, kTimeoutV, abortp) && ok;
+            ok = mbar_wait_abortable_a(cb(B_Q), n & 1, p.status, kTimeoutV, abortp) && ok;
             if (!ok) break;
             tc_fence_after_sync();
             GDN_OPHASE(0)
             GDN_TL(50 + warp - 8)
             const float* qf = reinterpret_cast<const float*>(sm + VEC + (n % kVecSlots) * 1024) + kChunk;   // scale e^gamma_i
-            uint32_t o[64];                               // -(S^T Q^T)[dv][j], taken as soon as it exists
+            uint32_t o[64];                               // (S^T Q^T)[dv][j], taken as soon as it exists
             {
                 uint32_t (&o0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&o[0]);
                 uint32_t (&o1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&o[32]);
@@ -319,7 +313,7 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
                         const float fq[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
-                            *drow = __float2bfloat16(fmaf(-fq[u], __uint_as_float(o[32 * h2 + j + u]), __uint_as_float(c[j + u])));
+                            *drow = __float2bfloat16(fmaf(fq[u], __uint_as_float(o[32 * h2 + j + u]), __uint_as_float(c[j + u])));
                             drow += row_stride;
                         }
                     }
@@ -327,7 +321,7 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         if (32 * h2 + j < valid)
-                            *drow = __float2bfloat16(fmaf(-qf[32 * h2 + j], __uint_as_float(o[32 * h2 + j]), __uint_as_float(c[j])));
+                            *drow = __float2bfloat16(fmaf(qf[32 * h2 + j], __uint_as_float(o[32 * h2 + j]), __uint_as_float(c[j])));
                         drow += row_stride;
                     }
                 }

@@ -102,8 +102,6 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const bool ok = head_is_splittable(ws.meta + seq * NT * 2, NT, ws.n_seg, L, lane, warm);
         if (lane == 0) split_ok = ok ? 1 : 0;
     }
-    chain_t::init_zero_blocks(sm, tid, chain_t::kThreads);
-    fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
