@@ -23,6 +23,12 @@
 namespace gdn {
 namespace {
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct QSmem {
     static constexpr uint32_t KQ = 0;                    // [K;Q]: 2 k-halves x 128 rows x 128 B (K rows 0-63, Q rows 64-127)
     static constexpr uint32_t YT = KQ + 8192;            // merge temporaries of head h at YT + h * 16384: Q's rows, dead after Q K^T
@@ -139,9 +145,12 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
         // the gate cumsum and the decay tables need nothing from the tiles: they run while the product does
         if (p.gate_act) prep_activate_gates(gv, bv);
-        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, ctx);
+        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, ctx, false);
         ctx.sync();
-        if (p.l2norm) prep_l2norm_fold(ps, kq, ws.vec + tile * 256, ctx);   // while the UMMAs run
+        if (p.l2norm) {   // while the UMMAs run
+            prep_l2norm_fold(ps, kq, ws.vec + tile * 256, ctx);
+            if (htid < kChunk) ps.ctab[0][htid] = ps.gam[htid] - __log2f(ps.rn[htid]);   // column table of the mask epilogue
+        }
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
         // the previous item's W stores must have finished reading their staging tiles (the T buffers) before those are
@@ -154,19 +163,21 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
         tc_fence_after_sync();
         {
-            float ri, diag[16];
-            if (p.l2norm) prep_row_setup_l2(ps, i, ri, diag);
-            else prep_row_setup(ps, i, ri, diag);
-            const float scale = p.l2norm ? scale0 * ps.rn[kChunk + i] : scale0;   // row factor of P
+            // Pairwise decay exp(gamma_i - gamma_j) for j <= i, one exponential per element (2^(g_i - g_j) with the
+            // cumsum kept in log2 units; the argument is <= 0 wherever the value is used, and what lies above the
+            // diagonal is selected away, never multiplied).  With L2 normalisation the column table carries
+            // -log2(1/|k_j|), so the same exponential also applies 1/|k_j|.
+            const float* gcol = p.l2norm ? ps.ctab[0] : ps.gam;
+            const float gi = ps.gam[i];
+            const bool low_rows = (hwarp & 1) == 0;          // rows 0-31: columns 32-63 lie above the diagonal
             uint32_t r[32];
-            float f[32];
             if (hwarp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
                 const float bi = p.l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
                 float ksq = 0.f;   // |k_i|^2: the diagonal of K K^T (for the decay bound of split sequences)
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
+                    if (half == 1 && low_rows) break;         // never read by the inverse
                     tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
-                    prep_row_factors(ps, i, half, ri, diag, f);
                     tmem_ld_wait();
                     if (ws.meta && (i >> 5) == half) {
 #pragma unroll
@@ -175,11 +186,12 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     }
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
+                        const float4 gj = *reinterpret_cast<const float4*>(gcol + half * 32 + c);
                         float4 o;
-                        o.x = (half * 32 + c + 0 < i) ? bi * f[c + 0] * __uint_as_float(r[c + 0]) : 0.f;
-                        o.y = (half * 32 + c + 1 < i) ? bi * f[c + 1] * __uint_as_float(r[c + 1]) : 0.f;
-                        o.z = (half * 32 + c + 2 < i) ? bi * f[c + 2] * __uint_as_float(r[c + 2]) : 0.f;
-                        o.w = (half * 32 + c + 3 < i) ? bi * f[c + 3] * __uint_as_float(r[c + 3]) : 0.f;
+                        o.x = (half * 32 + c + 0 < i) ? bi * fast_exp2(gi - gj.x) * __uint_as_float(r[c + 0]) : 0.f;
+                        o.y = (half * 32 + c + 1 < i) ? bi * fast_exp2(gi - gj.y) * __uint_as_float(r[c + 1]) : 0.f;
+                        o.z = (half * 32 + c + 2 < i) ? bi * fast_exp2(gi - gj.z) * __uint_as_float(r[c + 2]) : 0.f;
+                        o.w = (half * 32 + c + 3 < i) ? bi * fast_exp2(gi - gj.w) * __uint_as_float(r[c + 3]) : 0.f;
                         *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
                     }
                 }
@@ -192,19 +204,33 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     if (lane == 0) ps.wsum[hwarp] = bound;   // the cumsum's slots are free again by now
                 }
             } else {           // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
+                const float scale = p.l2norm ? scale0 * ps.rn[kChunk + i] : scale0;   // row factor of P
                 __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
+                    if (half == 1 && low_rows) {               // above the diagonal: zeros
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(prow + 32 + 8 * ch) = make_uint4(0, 0, 0, 0);
+                        break;
+                    }
                     tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
-                    prep_row_factors(ps, i, half, ri, diag, f);
                     tmem_ld_wait();
+                    float x[32];
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        const float4 gj = *reinterpret_cast<const float4*>(gcol + half * 32 + c);
+                        x[c + 0] = (half * 32 + c + 0 <= i) ? scale * fast_exp2(gi - gj.x) * __uint_as_float(r[c + 0]) : 0.f;
+                        x[c + 1] = (half * 32 + c + 1 <= i) ? scale * fast_exp2(gi - gj.y) * __uint_as_float(r[c + 1]) : 0.f;
+                        x[c + 2] = (half * 32 + c + 2 <= i) ? scale * fast_exp2(gi - gj.z) * __uint_as_float(r[c + 2]) : 0.f;
+                        x[c + 3] = (half * 32 + c + 3 <= i) ? scale * fast_exp2(gi - gj.w) * __uint_as_float(r[c + 3]) : 0.f;
+                    }
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) {
                         uint4 pk;
-                        pk.x = pack_bf16x2(scale * f[8 * ch + 0] * __uint_as_float(r[8 * ch + 0]), scale * f[8 * ch + 1] * __uint_as_float(r[8 * ch + 1]));
-                        pk.y = pack_bf16x2(scale * f[8 * ch + 2] * __uint_as_float(r[8 * ch + 2]), scale * f[8 * ch + 3] * __uint_as_float(r[8 * ch + 3]));
-                        pk.z = pack_bf16x2(scale * f[8 * ch + 4] * __uint_as_float(r[8 * ch + 4]), scale * f[8 * ch + 5] * __uint_as_float(r[8 * ch + 5]));
-                        pk.w = pack_bf16x2(scale * f[8 * ch + 6] * __uint_as_float(r[8 * ch + 6]), scale * f[8 * ch + 7] * __uint_as_float(r[8 * ch + 7]));
+                        pk.x = pack_bf16x2(x[8 * ch + 0], x[8 * ch + 1]);
+                        pk.y = pack_bf16x2(x[8 * ch + 2], x[8 * ch + 3]);
+                        pk.z = pack_bf16x2(x[8 * ch + 4], x[8 * ch + 5]);
+                        pk.w = pack_bf16x2(x[8 * ch + 6], x[8 * ch + 7]);
                         *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
                     }
                 }

@@ -71,8 +71,9 @@ __device__ __forceinline__ void prep_activate_gates(float& gv, float& bv) {
 // Contains two barriers of the group; a third one is needed before the tables are read.
 // If vec_out != nullptr, also writes the per-token factors a later kernel needs:
 //   vec_out[i] = exp(gamma_C - gamma_i), vec_out[64+i] = scale * exp(gamma_i), vec_out[128] = exp(gamma_C).
+// tables = false skips the block decay tables (ctab) for callers whose mask epilogue does not use them.
 __device__ __forceinline__ void prep_gates(PrepScratch& ps, float gv, float bv, float scale, float* vec_out,
-                                           PrepCtx ctx = PrepCtx::whole_cta()) {
+                                           PrepCtx ctx = PrepCtx::whole_cta(), bool tables = true) {
     const int tid = ctx.tid, warp = tid >> 5, lane = tid & 31;
     float gsum = 0.f;
     if (tid < kChunk) {
@@ -101,7 +102,7 @@ __device__ __forceinline__ void prep_gates(PrepScratch& ps, float gv, float bv, 
             if (tid == 0) vec_out[2 * kChunk] = exp2f(gC);
         }
     }
-    if (tid < 96) {   // 16 + 32 + 48 table entries
+    if (tables && tid < 96) {   // 16 + 32 + 48 table entries
         const int I = tid < 16 ? 1 : (tid < 48 ? 2 : 3);
         const int j = tid - (I == 1 ? 0 : (I == 2 ? 16 : 48));
         ps.ctab[I - 1][j] = exp2f(ps.gam[16 * I] - ps.gam[j]);
