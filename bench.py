@@ -42,7 +42,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per step of the dominant kernel, from the ncu captures summarised under
 # profiles/ (workload, kernel) -> bytes; anything not listed is reported as null
 DRAM_TRAFFIC = {
-    ("default", "gdn_chain_t_kernel"): 367.7e6,      # launch 1 (segments) 329.0 MB + launch 2 (first chunks again) 38.7 MB
+    ("default", "gdn_chain_t_kernel"): 358.8e6,      # 307.2 MB read + 51.6 MB written by the one split launch
     ("default", "gdn_chain_kernel"): 361.8e6,
     ("default", "gdn_coop_kernel"): 328.7e6,
 }
@@ -733,7 +733,7 @@ def main():
     single_launch = args.path == "coop" or (args.path == "auto" and w.S <= 2048 and 4 * B_local * w.Hv <= n_sm)
     transposed = args.path == "twopass_t" or (args.path == "auto" and not single_launch)
     kernels = ("gdn_coop_kernel (one launch)" if single_launch else
-               "gdn_prepare_kernel + gdn_chain_t_kernel (sequences split on the device: segments, then their first chunks again)"
+               "gdn_prepare_pair_kernel + gdn_chain_t_kernel (few long sequences are split into warmed-up segments on the device)"
                if transposed else
                "gdn_prepare_kernel + gdn_chain_kernel" if args.path in ("twopass_nv32", "twopass_nv64") else args.path)
     if transposed or args.path in ("twopass_nv32", "twopass_nv64"):
