@@ -51,10 +51,10 @@ constexpr uint32_t A_VS = 416;     // 32: bf16 v~^T
 constexpr uint32_t kTmemCols = 512;
 
 constexpr int kTimeoutFull = 0x401, kTimeoutEmpty = 0x402, kTimeoutV = 0x403, kTimeoutVN = 0x404, kTimeoutS = 0x405,
-              kTimeoutState = 0x406, kTimeoutO = 0x407, kTimeoutQsDone = 0x408, kTimeoutFlag = 0x409, kTimeoutPvDone = 0x40a;
+              kTimeoutState = 0x406, kTimeoutO = 0x407, kTimeoutQsDone = 0x408, kTimeoutFlag = 0x409, kTimeoutPvDone = 0x40a, kTimeoutVNP = 0x40b;
 
 // The CTA's barriers: kNumBars consecutive 8-byte mbarriers in shared memory, addressed by their shared-window address.
-enum : uint32_t { B_FULL = 0, B_EMPTY = kStages, B_V = 2 * kStages, B_Q, B_VN, B_S, B_STATE, B_O, B_QSDONE, B_PVDONE, kNumBars };
+enum : uint32_t { B_FULL = 0, B_EMPTY = kStages, B_V = 2 * kStages, B_Q, B_VN, B_VNP, B_S, B_STATE, B_O, B_QSDONE, B_PVDONE, kNumBars };
 struct Bars {
     uint32_t base;                     // shared-window address of barrier 0
     __device__ __forceinline__ uint32_t operator()(uint32_t i) const { return base + 8u * i; }
@@ -68,6 +68,7 @@ __device__ __forceinline__ void init_bars(uint64_t* bars) {   // one thread
     mbar_init(&bars[B_V], 1);
     mbar_init(&bars[B_Q], 1);
     mbar_init(&bars[B_VN], 8);
+    mbar_init(&bars[B_VNP], 8);
     mbar_init(&bars[B_S], 1);
     mbar_init(&bars[B_STATE], 8);
     mbar_init(&bars[B_O], 1);
@@ -223,6 +224,7 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
             GDN_TPHASE(5)
             GDN_TL(6)
             if (n > 0 && !mbar_wait_abortable_a(cb(B_PVDONE), (n - 1) & 1, p.status, kTimeoutPvDone, abortp)) break;
+            if (!mbar_wait_abortable_a(cb(B_VNP), n & 1, p.status, kTimeoutVNP, abortp)) break;   // the plain bf16 v_new^T is in place
             tc_fence_after_sync();
             GDN_TPHASE(6)
             GDN_TL(7)
@@ -378,31 +380,41 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
         tc_fence_after_sync();
         GDN_CPHASE(1)
         GDN_TL(10 + warp)
-        {   // v_new^T and v~^T of tokens [32 hf, +32) -> bf16 A operands
+        {   // v~^T, then v_new^T, of tokens [32 hf, +32) -> bf16 A operands.  E2 (the state's next term) waits for the
+            // scaled copy only; the plain copy, which only the output product E3 reads, follows behind a barrier of its own.
             uint32_t a0[16], a1[16];
             tmem_ld_x16(tmem_addr(tmem, lane_base, ACC_VQ + 32 * hf), a0);
             tmem_ld_x16(tmem_addr(tmem, lane_base, ACC_VQ + 32 * hf + 16), a1);
             tmem_ld_wait();
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
-                uint32_t pn[8], ps[8];
+                uint32_t ps[8];
 #pragma unroll
                 for (int c = 0; c < 8; c += 2) {
                     const float4 f = *reinterpret_cast<const float4*>(vec + 32 * hf + 16 * h2 + 2 * c);   // exp(gamma_C - gamma_j)
                     const float x0 = __uint_as_float(h2 ? a1[2 * c] : a0[2 * c]), x1 = __uint_as_float(h2 ? a1[2 * c + 1] : a0[2 * c + 1]);
                     const float x2 = __uint_as_float(h2 ? a1[2 * c + 2] : a0[2 * c + 2]), x3 = __uint_as_float(h2 ? a1[2 * c + 3] : a0[2 * c + 3]);
-                    pn[c] = pack_bf16x2(x0, x1);
-                    pn[c + 1] = pack_bf16x2(x2, x3);
                     ps[c] = pack_bf16x2(x0 * f.x, x1 * f.y);
                     ps[c + 1] = pack_bf16x2(x2 * f.z, x3 * f.w);
                 }
                 tmem_st_x8(tmem_addr(tmem, lane_base, A_VS + 16 * hf + 8 * h2), ps);
-                tmem_st_x8(tmem_addr(tmem, lane_base, A_VN + 16 * hf + 8 * h2), pn);
             }
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_a(cb(B_VN));
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+                uint32_t pn[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    pn[c] = pack_bf16x2(__uint_as_float(h2 ? a1[2 * c] : a0[2 * c]), __uint_as_float(h2 ? a1[2 * c + 1] : a0[2 * c + 1]));
+                tmem_st_x8(tmem_addr(tmem, lane_base, A_VN + 16 * hf + 8 * h2), pn);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_a(cb(B_VNP));
         }
         GDN_CPHASE(2)
         GDN_TL(20 + warp)
@@ -411,6 +423,7 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
         tc_fence_after_sync();
         GDN_CPHASE(3)
         GDN_TL(30 + warp)
+        const bool more = t + 1 < t1;
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {   // S^T <- exp(gamma_C) S^T + v~^T K, 32 columns at a time
             uint32_t r[32];
@@ -418,8 +431,19 @@ __device__ __forceinline__ void roles(uint8_t* sm, uint32_t sm_u32, uint32_t tme
             tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 32; ++c) st[32 * h2 + c] = fmaf(dC, st[32 * h2 + c], __uint_as_float(r[c]));
+            if (more) {                    // its bf16 copy goes out while the other half is loaded
+                uint32_t pk[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) pk[c] = pack_bf16x2(st[32 * h2 + 2 * c], st[32 * h2 + 2 * c + 1]);
+                tmem_st_x16(tmem_addr(tmem, lane_base, A_S + 32 * hf + 16 * h2), pk);
+            }
         }
-        if (t + 1 < t1) publish_state();
+        if (more) {
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_a(cb(B_STATE));
+        }
         GDN_CPHASE(4)
         GDN_TL(40 + warp)
     }

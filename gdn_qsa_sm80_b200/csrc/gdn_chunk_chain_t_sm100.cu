@@ -31,32 +31,29 @@ namespace {
 
 constexpr int kMaxSeg = 8;
 
-// One warp of a CTA: can this head be run as independent segments, and how many chunks of warm-up does segment s
-// need (warm[s], 1 <= s < G)?  meta: [NT][2] of this head.
-__device__ __forceinline__ bool head_is_splittable(const float* meta, int NT, int G, int L, int lane, int* warm) {
-    float bmax = 0.f;
-    for (int t = lane; t < NT; t += 32) bmax = fmaxf(bmax, meta[2 * t + 1]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
-    bool ok = bmax <= 2.f;            // false for NaN and for the +inf that marks a gate out of range
+// One warp of a CTA: with segment 0 = chunks [0, L0) and segment s >= 1 = L1 chunks from L0 + (s - 1) L1 on, how many
+// chunks of warm-up does segment s need (warm[s], 1 <= s < G)?  False if one of them has none within L1 chunks
+// (L1 <= L0, so that many chunks always lie before a boundary).  meta: [NT][2] of this head.
+__device__ __forceinline__ bool scan_warmups(const float* meta, int NT, int G, int L0, int L1, int lane, int* warm) {
+    bool ok = true;
     for (int s = 1; s < G; ++s) {
-        const int t0 = s * L;         // t0 >= L: at least L chunks lie before the boundary
+        const int t0 = L0 + (s - 1) * L1;
         if (t0 >= NT) {
             if (lane == 0) warm[s] = 0;
             continue;
         }
         int p = 0;
         float carry = 0.f;
-        for (int base = 0; base < L && p == 0; base += 32) {     // backwards from chunk t0 - 1, at most L chunks
+        for (int base = 0; base < L1 && p == 0; base += 32) {    // backwards from chunk t0 - 1, at most L1 chunks
             const int d = base + lane;
-            float x = d < L ? meta[2 * (t0 - 1 - d)] : 0.f;
+            float x = d < L1 ? meta[2 * (t0 - 1 - d)] : 0.f;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const float y = __shfl_up_sync(0xffffffffu, x, o);
                 if (lane >= o) x += y;
             }
             x += carry;
-            const unsigned below = __ballot_sync(0xffffffffu, d < L && x < kForgetLn);
+            const unsigned below = __ballot_sync(0xffffffffu, d < L1 && x < kForgetLn);
             if (below) p = base + __ffs(below);                  // chunks [t0 - p, t0) make the state forget
             carry = __shfl_sync(0xffffffffu, x, 31);
         }
@@ -64,6 +61,38 @@ __device__ __forceinline__ bool head_is_splittable(const float* meta, int NT, in
         if (lane == 0) warm[s] = p;
     }
     return ok;
+}
+
+// One warp of a CTA: can this head be run as G independent segments, and which ones?  Starts from equal segments of
+// L chunks; when those work, segment 0 (which has no warm-up) is lengthened and the others shortened so that every
+// CTA of the head runs about the same number of chunks, if the warm-ups at the moved boundaries allow it.
+// Every CTA of the head computes the same answer from the same scalars.  Result: lens[0] = L0, lens[1] = L1, warm[].
+__device__ __forceinline__ bool head_is_splittable(const float* meta, int NT, int G, int L, int lane, int* warm, int* lens) {
+    float bmax = 0.f;
+    for (int t = lane; t < NT; t += 32) bmax = fmaxf(bmax, meta[2 * t + 1]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+    if (lane == 0) lens[0] = lens[1] = L;
+    if (!(bmax <= 2.f)) return false;   // also for NaN and for the +inf that marks a gate out of range
+    if (!scan_warmups(meta, NT, G, L, L, lane, warm)) return false;
+    __syncwarp();
+    int pmax = 0;
+    for (int s = 1; s < G; ++s) pmax = max(pmax, warm[s]);
+    // equal work: L0 = L1 + p with L0 + (G - 1) L1 = NT
+    const int L1 = (NT - pmax + G - 1) / G, L0 = NT - (G - 1) * L1;
+    if (pmax < 2 || L1 < 1 || L0 <= L || L0 < L1) return true;
+    __shared__ int warm_moved[kMaxSeg];
+    if (!scan_warmups(meta, NT, G, L0, L1, lane, warm_moved)) return true;
+    __syncwarp();
+    int p2 = 0;
+    for (int s = 1; s < G; ++s) p2 = max(p2, warm_moved[s]);
+    if (max(L0, L1 + p2) >= L + pmax) return true;   // nothing gained
+    if (lane == 0) {
+        for (int s = 1; s < G; ++s) warm[s] = warm_moved[s];
+        lens[0] = L0;
+        lens[1] = L1;
+    }
+    return true;
 }
 
 // SPLIT = false: one CTA per sequence.  SPLIT = true: blockIdx.z = segment.
@@ -82,6 +111,7 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     __shared__ int abort_flag;
     __shared__ int split_ok;
     __shared__ int warm[kMaxSeg];
+    __shared__ int lens[2];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hv = blockIdx.x, b = blockIdx.y;
@@ -98,8 +128,9 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_alloc(&tmem_slot, chain_t::kTmemCols);
         tmem_relinquish();
     }
+    grid_dependency_wait();   // launched ahead of the end of the prepare kernel: nothing of the workspace is read above
     if (SPLIT && warp == 1) {
-        const bool ok = head_is_splittable(ws.meta + seq * NT * 2, NT, ws.n_seg, L, lane, warm);
+        const bool ok = head_is_splittable(ws.meta + seq * NT * 2, NT, ws.n_seg, L, lane, warm, lens);
         if (lane == 0) split_ok = ok ? 1 : 0;
     }
     tc_fence_before_sync();
@@ -115,7 +146,8 @@ gdn_chain_t_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         sp = chain_t::Span{0, NT, 0, h0, hT};
     } else {
         const int seg = static_cast<int>(blockIdx.z);
-        const int t0 = seg * L, t1 = min(NT, t0 + L);
+        const int t0 = seg == 0 ? 0 : lens[0] + (seg - 1) * lens[1];
+        const int t1 = min(NT, seg == 0 ? lens[0] : t0 + lens[1]);
         if (!split_ok) {
             if (seg == 0) sp = chain_t::Span{0, NT, 0, h0, hT};
         } else if (t0 < NT) {
@@ -153,9 +185,21 @@ int launch_chain_t(const Problem& p, const Workspace& ws, cudaStream_t stream) {
     const int NT = (p.S + kChunk - 1) / kChunk;
     auto go = [&](auto kernel, unsigned gz, int L) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return GDN_ERR_CUDA;
-        kernel<<<dim3(p.Hv, p.B, gz), chain_t::kThreads, smem, stream>>>(tq, tk, tv, tw, tp, tt2, p, ws, L);
+        // programmatic dependent launch: the CTAs may start (barriers, tensor memory) while the kernel before this one
+        // in the stream drains; the kernel waits for that kernel's completion before it reads anything
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(p.Hv, p.B, gz);
+        cfg.blockDim = dim3(chain_t::kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tq, tk, tv, tw, tp, tt2, p, ws, L);
         count_launch();
-        return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
+        return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };
     const int G = ws.n_seg;
     if (G <= 1 || G > kMaxSeg || !ws.meta) return go(gdn_chain_t_kernel<false>, 1, NT);

@@ -164,6 +164,9 @@ int gdn_chunk_fwd_host_sm100(const void* q, const void* k, const void* v, const 
 #define GDN_TRY(call) \
     if ((call) != cudaSuccess) return GDN_ERR_CUDA
 
+    // The copies and kernels of the call; a failure part-way leaves work on the copy streams, so the join below
+    // runs whatever this returns.
+    auto enqueue_all = [&]() -> int {
     // everything below is ordered after what the caller's stream holds so far (an earlier call's use of the arena included)
     GDN_TRY(cudaEventRecord(hp->start, stream));
     GDN_TRY(cudaStreamWaitEvent(hp->h2d, hp->start, 0));
@@ -211,13 +214,19 @@ int gdn_chunk_fwd_host_sm100(const void* q, const void* k, const void* v, const 
         }
         GDN_TRY(cudaMemcpyAsync(hT, state[n_seg & 1], state_bytes, cudaMemcpyDeviceToHost, hp->d2h));
     }
-    // the caller's stream continues only when every copy of this call is complete
-    GDN_TRY(cudaEventRecord(hp->done, hp->d2h));
-    GDN_TRY(cudaStreamWaitEvent(stream, hp->done, 0));
-    GDN_TRY(cudaEventRecord(hp->done, hp->h2d));
-    GDN_TRY(cudaStreamWaitEvent(stream, hp->done, 0));
-#undef GDN_TRY
     return GDN_OK;
+    };
+    const int st = enqueue_all();
+    // The caller's stream continues only when every copy this call enqueued is complete - also after an error, so
+    // that the caller may free or reuse the arena and the host buffers once its stream has drained.
+    auto join = [&](cudaStream_t copies) -> int {
+        GDN_TRY(cudaEventRecord(hp->done, copies));
+        GDN_TRY(cudaStreamWaitEvent(stream, hp->done, 0));
+        return GDN_OK;
+    };
+    const int j0 = join(hp->d2h), j1 = join(hp->h2d);
+#undef GDN_TRY
+    return st != GDN_OK ? st : (j0 != GDN_OK ? j0 : j1);
 }
 
 }  // extern "C"

@@ -106,6 +106,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         fence_mbar_init();
         issue_loads(cur);
     }
+    grid_launch_dependents();   // the chain kernel may set up its CTAs on SMs this grid has left
     if (warp == 0) {
         tmem_alloc(&tmem_slot, kPrepTmemCols);
         tmem_relinquish();

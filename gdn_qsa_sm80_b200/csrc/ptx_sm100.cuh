@@ -26,6 +26,21 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------------------------
+// In a kernel launched with the programmatic-stream-serialization attribute: blocks until the kernel before it in
+// the stream has completed and its writes are visible.  Everything above this call overlaps that kernel's tail.
+// A no-op in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next kernel of the stream, if it was launched with that attribute, begin its CTAs as SMs fall free
+// (they still wait in grid_dependency_wait for this grid to finish).  Takes effect once every CTA has called it or exited.
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -125,10 +140,13 @@ __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
 }
 __device__ __forceinline__ bool mbar_wait_abortable_a(uint32_t bar, uint32_t parity, int* status, int code,
                                                       volatile int* abort_flag) {
-    if (*abort_flag) return false;
+    // the barrier first: the abort flag costs a shared-memory round trip, which a wait on the critical path of a
+    // recurrence pays every time; a thread that runs one step past an abort only computes on stale data, and the
+    // status word already says so
 #pragma unroll 1
     for (int i = 0; i < 128; ++i)
         if (mbar_try_wait_a(bar, parity)) return true;
+    if (*abort_flag) return false;
     const unsigned long long t0 = globaltimer_ns();
 #pragma unroll 1
     while (true) {

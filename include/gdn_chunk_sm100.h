@@ -125,8 +125,11 @@ int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const vo
  * returns without waiting and everything enqueued on `stream` afterwards runs after the last output byte has
  * reached host memory - synchronise `stream` before reading out / hT on the host.  One status word at the
  * start of the arena collects the bounded-wait reports of all segments (gdn_chunk_read_status(arena, ...)).
- * Calls that share an arena must be issued on the same stream; calls with different arenas on different
- * streams overlap each other's copies.  flags as in gdn_chunk_fwd_sm100_ex.
+ * Calls that share an arena must be issued on the same stream.  Calls with different arenas on different
+ * streams may be in flight together: their kernels overlap the other call's copies, while the copies
+ * themselves share one queue per direction and device (one internal stream each way).  After an error return
+ * the caller's stream is still ordered behind every copy the call had enqueued.
+ * flags as in gdn_chunk_fwd_sm100_ex.
  * Replaces what a caller of the reference writes around it by hand: `.cuda()` on every input, the operator,
  * `.cpu()` on the results (the reference's benchmarks create their tensors on the device,
  * benchmarks/bench_gdn_chunk.py:23-27, and leave the host link out of the picture).

@@ -76,8 +76,8 @@ def test_chained_behind_the_forward_pass(path, S):
 
 
 def test_behind_the_transposed_chain_with_split_sequences():
-    """Long sequences, few heads: the transposed chain splits them on the device (two launches that both write
-    outputs); the gate behind them gives the same bits as the forward pass followed by the separate call."""
+    """Long sequences, few heads: the transposed chain splits them on the device (segments with unstored
+    warm-up chunks); the gate behind it gives the same bits as the forward pass followed by the separate call."""
     S = 4096
     q, k, v, g, beta, h0 = make_inputs("default", seed=31, B=1, S=S, Hq=4, Hv=8)
     gen = torch.Generator().manual_seed(32)
