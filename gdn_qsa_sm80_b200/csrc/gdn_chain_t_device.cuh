@@ -12,7 +12,9 @@
 //        S^T <- exp(gamma_C) S^T + ACC_S                                                                   (ref :94)
 //   E3   ACC_PV = v_new^T P^T           (A = bf16 v_new^T in TMEM, B = P as loaded)
 //        O^T = scale exp(gamma_i) (S^T Q^T) + ACC_PV  (column factors)                                   (ref :92-93)
-// 28 UMMA instructions per chunk, of which the 8 of E1 and the 4 of E2 are on the critical path.
+// 28 UMMA instructions per chunk, of which the 8 of E1 and the 4 of E2 are on the critical path.  What the critical
+// warps hand over is ordered by who waits for it: the decay-scaled v~^T first (E2), the plain v_new^T behind a barrier
+// of its own (E3, an output product), each half of the state's bf16 copy as soon as that half is updated.
 // Nothing the recurrence produces is written to shared memory, no generic-to-async proxy fence sits on the critical
 // path, and one CTA carries all 128 value columns of a head, so every workspace tile is read once per head.
 // The reference keeps its state in registers for the same reason (csrc/gdn_chunk/gdn_kernel.cu:1581-1606).

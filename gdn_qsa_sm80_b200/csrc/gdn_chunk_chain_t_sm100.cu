@@ -16,7 +16,8 @@
 // scalars the prepare kernel left (ws.meta):
 //   * if every segment s >= 1 has such a warm-up no longer than a segment and the premise on beta |k|^2 holds on
 //     every chunk, the G CTAs of the head run their segments at once (segment 0 from the caller's initial state, the
-//     last one writes the final state);
+//     last one writes the final state); segment 0, which has no warm-up, is then made longer and the others shorter
+//     so that all G CTAs run about the same number of chunks, when the warm-ups at the moved boundaries allow it;
 //   * otherwise the CTA of segment 0 runs the whole sequence serially and the others return at once.
 // No host read, no data-dependent launch, no state passed between CTAs; results equal the serial chain's.
 #include <cuda.h>
