@@ -23,12 +23,6 @@
 namespace gdn {
 namespace {
 
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 struct QSmem {
     static constexpr uint32_t KQ = 0;                    // [K;Q]: 2 k-halves x 128 rows x 128 B (K rows 0-63, Q rows 64-127)
     static constexpr uint32_t YT = KQ + 8192;            // merge temporaries of head h at YT + h * 16384: Q's rows, dead after Q K^T
@@ -163,78 +157,21 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         prep_zero_upper_blocks(Tm, ctx);
 
         tc_fence_after_sync();
-        {
-            // Pairwise decay exp(gamma_i - gamma_j) for j <= i, one exponential per element (2^(g_i - g_j) with the
-            // cumsum kept in log2 units; the argument is <= 0 wherever the value is used, and what lies above the
-            // diagonal is selected away, never multiplied).  With L2 normalisation the column table carries
-            // -log2(1/|k_j|), so the same exponential also applies 1/|k_j|.
-            const float* gcol = p.l2norm ? ps.ctab[0] : ps.gam;
-            const float gi = ps.gam[i];
+        {   // mask epilogue (one exponential per element, shared with gdn_prepare_kernel): thread = row i = TMEM lane
             const bool low_rows = (hwarp & 1) == 0;          // rows 0-31: columns 32-63 lie above the diagonal
-            uint32_t r[32];
             if (hwarp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
-                const float bi = p.l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
-                float ksq = 0.f;   // |k_i|^2: the diagonal of K K^T (for the decay bound of split sequences)
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    if (half == 1 && low_rows) break;         // never read by the inverse
-                    tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
-                    tmem_ld_wait();
-                    if (ws.meta && (i >> 5) == half) {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (c == (i & 31)) ksq = __uint_as_float(r[c]);
-                    }
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        const float4 gj = *reinterpret_cast<const float4*>(gcol + half * 32 + c);
-                        float4 o;
-                        o.x = (half * 32 + c + 0 < i) ? bi * fast_exp2(gi - gj.x) * __uint_as_float(r[c + 0]) : 0.f;
-                        o.y = (half * 32 + c + 1 < i) ? bi * fast_exp2(gi - gj.y) * __uint_as_float(r[c + 1]) : 0.f;
-                        o.z = (half * 32 + c + 2 < i) ? bi * fast_exp2(gi - gj.z) * __uint_as_float(r[c + 2]) : 0.f;
-                        o.w = (half * 32 + c + 3 < i) ? bi * fast_exp2(gi - gj.w) * __uint_as_float(r[c + 3]) : 0.f;
-                        *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
-                    }
-                }
+                const float ksq = prep_mask_row_A(ps, p.l2norm != 0, tmem_addr(tmem, lane_base, 0), i, low_rows, As, ws.meta != nullptr);
                 if (ws.meta) {   // max over the chunk of beta_i |k_i|^2, +inf when a gate is outside beta >= 0, g <= 0
-                    const float rk = p.l2norm ? ps.rn[i] : 1.f;
-                    const bool in_range = ps.bet[i] >= 0.f && ps.gam[i] <= (i > 0 ? ps.gam[i - 1] : 0.f);
-                    float bound = in_range ? ps.bet[i] * ksq * rk * rk : INFINITY;
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, o));
+                    const float bound = prep_bound_of_rows(ps, p.l2norm != 0, i, ksq);
                     if (lane == 0) ps.wsum[hwarp] = bound;   // the cumsum's slots are free again by now
                 }
+                // the 32 x 32 diagonal block of T over this warp's own rows needs nobody else: no barrier, and it runs
+                // while the other warps are still in their part of the mask epilogue
+                __syncwarp();
+                prep_invert_diag32(As, Tm, Yt + 512 * hwarp, hwarp, lane);
             } else {           // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
-                const float scale = p.l2norm ? scale0 * ps.rn[kChunk + i] : scale0;   // row factor of P
-                __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    if (half == 1 && low_rows) {               // above the diagonal: zeros
-#pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(prow + 32 + 8 * ch) = make_uint4(0, 0, 0, 0);
-                        break;
-                    }
-                    tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
-                    tmem_ld_wait();
-                    float x[32];
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        const float4 gj = *reinterpret_cast<const float4*>(gcol + half * 32 + c);
-                        x[c + 0] = (half * 32 + c + 0 <= i) ? scale * fast_exp2(gi - gj.x) * __uint_as_float(r[c + 0]) : 0.f;
-                        x[c + 1] = (half * 32 + c + 1 <= i) ? scale * fast_exp2(gi - gj.y) * __uint_as_float(r[c + 1]) : 0.f;
-                        x[c + 2] = (half * 32 + c + 2 <= i) ? scale * fast_exp2(gi - gj.z) * __uint_as_float(r[c + 2]) : 0.f;
-                        x[c + 3] = (half * 32 + c + 3 <= i) ? scale * fast_exp2(gi - gj.w) * __uint_as_float(r[c + 3]) : 0.f;
-                    }
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint4 pk;
-                        pk.x = pack_bf16x2(x[8 * ch + 0], x[8 * ch + 1]);
-                        pk.y = pack_bf16x2(x[8 * ch + 2], x[8 * ch + 3]);
-                        pk.z = pack_bf16x2(x[8 * ch + 4], x[8 * ch + 5]);
-                        pk.w = pack_bf16x2(x[8 * ch + 6], x[8 * ch + 7]);
-                        *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
-                    }
-                }
+                prep_mask_row_P(ps, p.l2norm != 0, scale0, tmem_addr(tmem, lane_base, 0), i, low_rows,
+                                ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
             }
         }
         GDN_PHASE(2)
@@ -246,7 +183,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
 
         GDN_PHASE(3)
-        prep_invert_unit_lower(As, Tm, Yt, ctx);
+        prep_invert_level2(As, Tm, Yt, ctx);
         GDN_PHASE(4)
 
         // both heads are done with their A matrices (the stacked operand lies over head a's) and with the raw

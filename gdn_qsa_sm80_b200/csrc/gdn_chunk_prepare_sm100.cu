@@ -129,7 +129,7 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (; L < num_tiles && ok; L += gridDim.x) {
         const size_t tile = cur.ws_tile;
         if (p.gate_act) prep_activate_gates(gv, bv);
-        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256);
+        prep_gates(ps, gv, bv, scale0, ws.vec + tile * 256, PrepCtx::whole_cta(), false);
         __syncthreads();
         GDN_PHASE(0)
 
@@ -149,7 +149,10 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             umma_commit(&bar_mma);
         }
-        if (p.l2norm) prep_l2norm_fold(ps, sm + PSmem::KQ, ws.vec + tile * 256);   // while the UMMAs run
+        if (p.l2norm) {   // while the UMMAs run
+            prep_l2norm_fold(ps, sm + PSmem::KQ, ws.vec + tile * 256);
+            if (tid < kChunk) ps.ctab[0][tid] = ps.gam[tid] - __log2f(ps.rn[tid]);   // column table of the mask epilogue
+        }
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
         // the previous tile's W/U stores must have finished reading their staging tiles (the T and A buffers) before
@@ -165,61 +168,18 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         prep_zero_upper_blocks(Tm);   // the T buffer held the previous tile's W staging tile until the wait above
 
         tc_fence_after_sync();
-        {
-            float ri, diag[16];
-            if (p.l2norm) prep_row_setup_l2(ps, i, ri, diag);
-            else prep_row_setup(ps, i, ri, diag);
-            const float scale = p.l2norm ? scale0 * ps.rn[kChunk + i] : scale0;   // row factor of P
-            uint32_t r[32];
-            float f[32];
+        {   // mask epilogue (one exponential per element, shared with gdn_prepare_pair_kernel, so that both kernels
+            // produce the same bits): thread = row i = TMEM lane
+            const bool low_rows = (warp & 1) == 0;           // rows 0-31: columns 32-63 lie above the diagonal
             if (warp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
-                const float bi = p.l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
-                float ksq = 0.f;   // |k_i|^2: the diagonal of K K^T (only for the decay bound of split sequences)
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
-                    prep_row_factors(ps, i, half, ri, diag, f);
-                    tmem_ld_wait();
-                    if (ws.meta && (i >> 5) == half) {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (c == (i & 31)) ksq = __uint_as_float(r[c]);
-                    }
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        float4 o;
-                        o.x = (half * 32 + c + 0 < i) ? bi * f[c + 0] * __uint_as_float(r[c + 0]) : 0.f;
-                        o.y = (half * 32 + c + 1 < i) ? bi * f[c + 1] * __uint_as_float(r[c + 1]) : 0.f;
-                        o.z = (half * 32 + c + 2 < i) ? bi * f[c + 2] * __uint_as_float(r[c + 2]) : 0.f;
-                        o.w = (half * 32 + c + 3 < i) ? bi * f[c + 3] * __uint_as_float(r[c + 3]) : 0.f;
-                        *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
-                    }
-                }
-                if (ws.meta) {   // max over the chunk of beta_i |k_i|^2, +inf when a gate is outside beta >= 0, g <= 0
-                    const float rk = p.l2norm ? ps.rn[i] : 1.f;
-                    const bool in_range = ps.bet[i] >= 0.f && ps.gam[i] <= (i > 0 ? ps.gam[i - 1] : 0.f);
-                    float bound = in_range ? ps.bet[i] * ksq * rk * rk : INFINITY;
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, o));
+                const float ksq = prep_mask_row_A(ps, p.l2norm != 0, tmem_addr(tmem, lane_base, 0), i, low_rows, As, ws.meta != nullptr);
+                if (ws.meta) {
+                    const float bound = prep_bound_of_rows(ps, p.l2norm != 0, i, ksq);
                     if ((tid & 31) == 0) ps.wsum[warp] = bound;   // the cumsum's slots are free again by now
                 }
             } else {          // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
-                __nv_bfloat16* prow = ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk;
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    tmem_ld_x32(tmem_addr(tmem, lane_base, half * 32), r);
-                    prep_row_factors(ps, i, half, ri, diag, f);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint4 pk;
-                        pk.x = pack_bf16x2(scale * f[8 * ch + 0] * __uint_as_float(r[8 * ch + 0]), scale * f[8 * ch + 1] * __uint_as_float(r[8 * ch + 1]));
-                        pk.y = pack_bf16x2(scale * f[8 * ch + 2] * __uint_as_float(r[8 * ch + 2]), scale * f[8 * ch + 3] * __uint_as_float(r[8 * ch + 3]));
-                        pk.z = pack_bf16x2(scale * f[8 * ch + 4] * __uint_as_float(r[8 * ch + 4]), scale * f[8 * ch + 5] * __uint_as_float(r[8 * ch + 5]));
-                        pk.w = pack_bf16x2(scale * f[8 * ch + 6] * __uint_as_float(r[8 * ch + 6]), scale * f[8 * ch + 7] * __uint_as_float(r[8 * ch + 7]));
-                        *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
-                    }
-                }
+                prep_mask_row_P(ps, p.l2norm != 0, scale0, tmem_addr(tmem, lane_base, 0), i, low_rows,
+                                ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
             }
         }
         tc_fence_before_sync();

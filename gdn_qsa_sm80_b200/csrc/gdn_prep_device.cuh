@@ -232,29 +232,125 @@ __device__ __forceinline__ void store_c_frag(float* m, int ld, int lane, const f
     *reinterpret_cast<float2*>(m + (g + 8) * ld + 2 * t) = make_float2(sign * c[2], sign * c[3]);
 }
 
-// T = (I + A)^-1 for the strictly lower-triangular 64x64 A in `As` (fp32, row stride kSolveStride).
-// Result in `Tm` (same layout; must be zero above the 16x16 diagonal blocks on entry - the caller zeroes it).
-// `Yt` is a scratch of at least 32*kY2Stride floats.  Blocked inversion:
-//   16x16 diagonal blocks by forward substitution in fp32 registers, then
-//   [[L11,0],[L21,L22]]^-1 = [[X11,0],[-X22 L21 X11, X22]] at block sizes 16 and 32 with TF32 warp MMAs.
-// Contains its own barriers; `As` and `Tm` must be complete before the call (one barrier before).
-__device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* Tm, float* Yt,
-                                                       PrepCtx ctx = PrepCtx::whole_cta()) {
-    const int tid = ctx.tid, warp = tid >> 5, lane = tid & 31;
-    if (tid < 64) {
-        const int blk = tid >> 4, c = tid & 15;
-        const float* a = As + (16 * blk) * kSolveStride + 16 * blk;
-        float4 rowv[15][4];
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Mask epilogue, one exponential per element.  The pairwise decay exp(gamma_i - gamma_j) for j <= i is
+// 2^(g_i - g_j) with the cumsum kept in log2 units; the argument is <= 0 wherever the value is used, and what lies
+// above the diagonal is selected away, never multiplied.  With L2 normalisation the column table ps.ctab[0] carries
+// g_j - log2(1/|k_j|) (the caller fills it), so the same exponential also applies 1/|k_j|.
+// Thread = row i = one TMEM lane; `trow` = tensor-memory address of column 0 of the warp's lanes; low_rows (warp-uniform):
+// the warp's rows are 0-31, whose columns 32-63 lie above the diagonal.
+
+// Raw K K^T row -> row i of A = tril(beta_i * decay * K K^T, -1), fp32, into `As` (columns 32-63 of rows 0-31 are
+// not written: the inverse never reads them).  Returns |k_i|^2 (the diagonal entry) when want_ksq.
+__device__ __forceinline__ float prep_mask_row_A(const PrepScratch& ps, bool l2norm, uint32_t trow, int i, bool low_rows,
+                                                 float* As, bool want_ksq) {
+    const float* gcol = l2norm ? ps.ctab[0] : ps.gam;
+    const float gi = ps.gam[i];
+    const float bi = l2norm ? ps.bet[i] * ps.rn[i] : ps.bet[i];
+    float ksq = 0.f;
+    uint32_t r[32];
 #pragma unroll
-        for (int i = 1; i < 16; ++i)
+    for (int half = 0; half < 2; ++half) {
+        if (half == 1 && low_rows) break;
+        tmem_ld_x32(trow + half * 32, r);
+        tmem_ld_wait();
+        if (want_ksq && (i >> 5) == half) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
+            for (int c = 0; c < 32; ++c)
+                if (c == (i & 31)) ksq = __uint_as_float(r[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+            const float4 gj = *reinterpret_cast<const float4*>(gcol + half * 32 + c);
+            float4 o;
+            o.x = (half * 32 + c + 0 < i) ? bi * fast_exp2(gi - gj.x) * __uint_as_float(r[c + 0]) : 0.f;
+            o.y = (half * 32 + c + 1 < i) ? bi * fast_exp2(gi - gj.y) * __uint_as_float(r[c + 1]) : 0.f;
+            o.z = (half * 32 + c + 2 < i) ? bi * fast_exp2(gi - gj.z) * __uint_as_float(r[c + 2]) : 0.f;
+            o.w = (half * 32 + c + 3 < i) ? bi * fast_exp2(gi - gj.w) * __uint_as_float(r[c + 3]) : 0.f;
+            *reinterpret_cast<float4*>(As + i * kSolveStride + half * 32 + c) = o;
+        }
+    }
+    return ksq;
+}
+
+// max over the warp's rows of beta_i |k_i|^2 (the premise of the decay bound for split sequences), +inf when a gate
+// of the row is outside beta >= 0, g <= 0.  ksq: the raw diagonal entry of K K^T.
+__device__ __forceinline__ float prep_bound_of_rows(const PrepScratch& ps, bool l2norm, int i, float ksq) {
+    const float rk = l2norm ? ps.rn[i] : 1.f;
+    const bool in_range = ps.bet[i] >= 0.f && ps.gam[i] <= (i > 0 ? ps.gam[i - 1] : 0.f);
+    float bound = in_range ? ps.bet[i] * ksq * rk * rk : INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, o));
+    return bound;
+}
+
+// Raw Q K^T row -> row i of P = tril(scale * decay * Q K^T), bf16, straight to the workspace (`prow`: 64 values).
+// The row factor (positive) travels in the exponent.
+__device__ __forceinline__ void prep_mask_row_P(const PrepScratch& ps, bool l2norm, float scale0, uint32_t trow, int i,
+                                                bool low_rows, __nv_bfloat16* prow) {
+    const float* gcol = l2norm ? ps.ctab[0] : ps.gam;
+    const float gis = ps.gam[i] + __log2f(l2norm ? scale0 * ps.rn[kChunk + i] : scale0);
+    uint32_t r[32];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        if (half == 1 && low_rows) {               // above the diagonal: zeros
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(prow + 32 + 8 * ch) = make_uint4(0, 0, 0, 0);
+            break;
+        }
+        tmem_ld_x32(trow + half * 32, r);
+        tmem_ld_wait();
+        float x[32];
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+            const float4 gj = *reinterpret_cast<const float4*>(gcol + half * 32 + c);
+            x[c + 0] = (half * 32 + c + 0 <= i) ? fast_exp2(gis - gj.x) * __uint_as_float(r[c + 0]) : 0.f;
+            x[c + 1] = (half * 32 + c + 1 <= i) ? fast_exp2(gis - gj.y) * __uint_as_float(r[c + 1]) : 0.f;
+            x[c + 2] = (half * 32 + c + 2 <= i) ? fast_exp2(gis - gj.z) * __uint_as_float(r[c + 2]) : 0.f;
+            x[c + 3] = (half * 32 + c + 3 <= i) ? fast_exp2(gis - gj.w) * __uint_as_float(r[c + 3]) : 0.f;
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            uint4 pk;
+            pk.x = pack_bf16x2(x[8 * ch + 0], x[8 * ch + 1]);
+            pk.y = pack_bf16x2(x[8 * ch + 2], x[8 * ch + 3]);
+            pk.z = pack_bf16x2(x[8 * ch + 4], x[8 * ch + 5]);
+            pk.w = pack_bf16x2(x[8 * ch + 6], x[8 * ch + 7]);
+            *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
+        }
+    }
+}
+
+// Blocked inversion of T = (I + A)^-1 for the strictly lower-triangular 64x64 A in `As` (fp32, row stride
+// kSolveStride), result in `Tm` (same layout):
+//   8x8 diagonal blocks by forward substitution in fp32 registers, then
+//   [[L11,0],[L21,L22]]^-1 = [[X11,0],[-X22 L21 X11, X22]] at block size 8 in fp32 and at block sizes 16 and 32 with
+//   TF32 warp MMAs.
+// Everything up to the two 32x32 diagonal blocks involves only 32 consecutive rows, so ONE WARP does it for the rows
+// it owns with no CTA-level barrier (prep_invert_diag32); only the last level crosses (prep_invert_level2).
+
+// One warp: the 32x32 diagonal block p (rows and columns 32p .. 32p+31) of T.  Needs rows 32p .. 32p+31 of `As`
+// visible to the warp (after the warp's own writes a __syncwarp is enough).  `y`: 448 floats of scratch of its own.
+__device__ __forceinline__ void prep_invert_diag32(const float* As, float* Tm, float* y, int p, int lane) {
+    {   // four 8x8 diagonal blocks: lane = (block, column), forward substitution in registers
+        const int blk = 4 * p + (lane >> 3), c = lane & 7;
+        const float* a = As + (8 * blk) * kSolveStride + 8 * blk;
+        float4 rowv[7][2];
+#pragma unroll
+        for (int i = 1; i < 8; ++i)
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
                 if (4 * q < i) rowv[i - 1][q] = *reinterpret_cast<const float4*>(a + i * kSolveStride + 4 * q);
-        float x[16];
+        float x[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = (i == c) ? 1.f : 0.f;
+        for (int i = 0; i < 8; ++i) x[i] = (i == c) ? 1.f : 0.f;
 #pragma unroll
-        for (int i = 1; i < 16; ++i) {
+        for (int i = 1; i < 8; ++i) {
             float acc0 = x[i], acc1 = 0.f;
 #pragma unroll
             for (int j = 0; j < i; ++j) {
@@ -266,67 +362,131 @@ __device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* T
             x[i] = acc0 + acc1;
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) Tm[(16 * blk + i) * kSolveStride + 16 * blk + c] = x[i];
+        for (int i = 0; i < 8; ++i) Tm[(8 * blk + i) * kSolveStride + 8 * blk + c] = x[i];
+        // zeros in the upper-right 8x8 of the two 16x16 diagonal blocks (one float4 per lane)
+        const int b16 = 2 * p + (lane >> 4), r = (lane >> 1) & 7, q = lane & 1;
+        *reinterpret_cast<float4*>(Tm + (16 * b16 + r) * kSolveStride + 16 * b16 + 8 + 4 * q) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    ctx.sync();
-    {   // level 1: pairs of 16-blocks.  warp -> (pair p, 8-column tile nt)
-        const int p = warp >> 1, nt = warp & 1;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    __syncwarp();
+    {   // 8 -> 16 in fp32: X21 = -X22 (A21 X11).  lane = (16-block, row r, four columns c0 ..) of the 8x8 result
+        const int b16 = 2 * p + (lane >> 4), r = (lane >> 1) & 7, c0 = 4 * (lane & 1);
+        const float* a21 = As + (16 * b16 + 8 + r) * kSolveStride + 16 * b16;
+        const float* x11 = Tm + (16 * b16) * kSolveStride + 16 * b16 + c0;
+        const float* x22 = Tm + (16 * b16 + 8 + r) * kSolveStride + 16 * b16 + 8;
+        float* yb = y + 64 * (lane >> 4);
+        {
+            const float4 a0 = *reinterpret_cast<const float4*>(a21), a1 = *reinterpret_cast<const float4*>(a21 + 4);
+            const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-            uint32_t a[4], b[2];
-            load_a_frag(a, As + (32 * p + 16) * kSolveStride + 32 * p + 8 * ks, kSolveStride, lane);
-            load_b_frag(b, Tm + (32 * p + 8 * ks) * kSolveStride + 32 * p + 8 * nt, kSolveStride, lane);
-            mma_tf32_16x8x8(acc, a, b);
+            for (int k = 0; k < 8; ++k) {
+                const float4 xv = *reinterpret_cast<const float4*>(x11 + k * kSolveStride);
+                acc.x = fmaf(av[k], xv.x, acc.x);
+                acc.y = fmaf(av[k], xv.y, acc.y);
+                acc.z = fmaf(av[k], xv.z, acc.z);
+                acc.w = fmaf(av[k], xv.w, acc.w);
+            }
+            *reinterpret_cast<float4*>(yb + 8 * r + c0) = acc;
         }
-        store_c_frag(Yt + (16 * p) * kY1Stride + 8 * nt, kY1Stride, lane, acc, 1.f);
-        ctx.sync();
-        float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+        __syncwarp();
+        {
+            const float4 b0 = *reinterpret_cast<const float4*>(x22), b1 = *reinterpret_cast<const float4*>(x22 + 4);
+            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-            uint32_t a[4], b[2];
-            load_a_frag(a, Tm + (32 * p + 16) * kSolveStride + 32 * p + 16 + 8 * ks, kSolveStride, lane);
-            load_b_frag(b, Yt + (16 * p + 8 * ks) * kY1Stride + 8 * nt, kY1Stride, lane);
-            mma_tf32_16x8x8(acc2, a, b);
+            for (int k = 0; k < 8; ++k) {
+                const float4 yv = *reinterpret_cast<const float4*>(yb + 8 * k + c0);
+                acc.x = fmaf(-bv[k], yv.x, acc.x);
+                acc.y = fmaf(-bv[k], yv.y, acc.y);
+                acc.z = fmaf(-bv[k], yv.z, acc.z);
+                acc.w = fmaf(-bv[k], yv.w, acc.w);
+            }
+            *reinterpret_cast<float4*>(Tm + (16 * b16 + 8 + r) * kSolveStride + 16 * b16 + c0) = acc;
         }
-        store_c_frag(Tm + (32 * p + 16) * kSolveStride + 32 * p + 8 * nt, kSolveStride, lane, acc2, -1.f);
     }
-    ctx.sync();
-    {   // level 2: the 32x32 lower-left block.  warp -> (16-row block rb, 16-column block cb)
-        const int rb = warp >> 1, cb = warp & 1;
+    __syncwarp();
+    {   // 16 -> 32 with TF32 warp MMAs: Y = A21 X11, X21 = -X22 Y (16 x 16 each)
+        float* y1 = y + 128;
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
+        for (int ks = 0; ks < 2; ++ks) {
             uint32_t a[4];
-            load_a_frag(a, As + (32 + 16 * rb) * kSolveStride + 8 * ks, kSolveStride, lane);
+            load_a_frag(a, As + (32 * p + 16) * kSolveStride + 32 * p + 8 * ks, kSolveStride, lane);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 uint32_t b[2];
-                load_b_frag(b, Tm + (8 * ks) * kSolveStride + 16 * cb + 8 * nt, kSolveStride, lane);
+                load_b_frag(b, Tm + (32 * p + 8 * ks) * kSolveStride + 32 * p + 8 * nt, kSolveStride, lane);
                 mma_tf32_16x8x8(acc[nt], a, b);
             }
         }
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-            store_c_frag(Yt + (16 * rb) * kY2Stride + 16 * cb + 8 * nt, kY2Stride, lane, acc[nt], 1.f);
-        ctx.sync();
+        for (int nt = 0; nt < 2; ++nt) store_c_frag(y1 + 8 * nt, kY1Stride, lane, acc[nt], 1.f);
+        __syncwarp();
         float acc2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
+        for (int ks = 0; ks < 2; ++ks) {
             uint32_t a[4];
-            load_a_frag(a, Tm + (32 + 16 * rb) * kSolveStride + 32 + 8 * ks, kSolveStride, lane);
+            load_a_frag(a, Tm + (32 * p + 16) * kSolveStride + 32 * p + 16 + 8 * ks, kSolveStride, lane);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 uint32_t b[2];
-                load_b_frag(b, Yt + (8 * ks) * kY2Stride + 16 * cb + 8 * nt, kY2Stride, lane);
+                load_b_frag(b, y1 + (8 * ks) * kY1Stride + 8 * nt, kY1Stride, lane);
                 mma_tf32_16x8x8(acc2[nt], a, b);
             }
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
-            store_c_frag(Tm + (32 + 16 * rb) * kSolveStride + 16 * cb + 8 * nt, kSolveStride, lane, acc2[nt], -1.f);
+            store_c_frag(Tm + (32 * p + 16) * kSolveStride + 32 * p + 8 * nt, kSolveStride, lane, acc2[nt], -1.f);
     }
+}
+
+// All 128 threads: the 32x32 lower-left block of T, X21 = -X22 (A21 X11), from the two diagonal blocks (which must be
+// complete: one barrier before).  `Yt`: 32*kY2Stride floats.  Ends with a barrier.  warp -> (16-row block rb, 16-column block cb)
+__device__ __forceinline__ void prep_invert_level2(const float* As, float* Tm, float* Yt, PrepCtx ctx = PrepCtx::whole_cta()) {
+    const int tid = ctx.tid, warp = tid >> 5, lane = tid & 31;
+    const int rb = warp >> 1, cb = warp & 1;
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        uint32_t a[4];
+        load_a_frag(a, As + (32 + 16 * rb) * kSolveStride + 8 * ks, kSolveStride, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            uint32_t b[2];
+            load_b_frag(b, Tm + (8 * ks) * kSolveStride + 16 * cb + 8 * nt, kSolveStride, lane);
+            mma_tf32_16x8x8(acc[nt], a, b);
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+        store_c_frag(Yt + (16 * rb) * kY2Stride + 16 * cb + 8 * nt, kY2Stride, lane, acc[nt], 1.f);
     ctx.sync();
+    float acc2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        uint32_t a[4];
+        load_a_frag(a, Tm + (32 + 16 * rb) * kSolveStride + 32 + 8 * ks, kSolveStride, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            uint32_t b[2];
+            load_b_frag(b, Yt + (8 * ks) * kY2Stride + 16 * cb + 8 * nt, kY2Stride, lane);
+            mma_tf32_16x8x8(acc2[nt], a, b);
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+        store_c_frag(Tm + (32 + 16 * rb) * kSolveStride + 16 * cb + 8 * nt, kSolveStride, lane, acc2[nt], -1.f);
+    ctx.sync();
+}
+
+// The whole inversion by 128 threads.  `Tm` must be zero above the 16x16 diagonal blocks on entry (the caller zeroes
+// it), `As` complete (one barrier before).  `Yt`: scratch of at least 32*kY2Stride floats.
+__device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* Tm, float* Yt,
+                                                       PrepCtx ctx = PrepCtx::whole_cta()) {
+    const int warp = ctx.tid >> 5, lane = ctx.tid & 31;
+    if (warp < 2) prep_invert_diag32(As, Tm, Yt + 512 * warp, warp, lane);
+    ctx.sync();
+    prep_invert_level2(As, Tm, Yt, ctx);
 }
 
 // Zeroes the six 16x16 blocks of `Tm` above the block diagonal (all 128 threads; what prep_invert_unit_lower
