@@ -148,13 +148,12 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
-        // the previous item's W stores must have finished reading their staging tiles (the T buffers) before those are
-        // zeroed below
+        // the previous item's W stores must have finished reading their staging tiles (the T buffers) before the
+        // inverse writes them again
         if (tid == 0) tma_store_wait_read();
         ok = __syncthreads_and(ok);
         if (!ok) break;
         GDN_PHASE(1)
-        prep_zero_upper_blocks(Tm, ctx);
 
         tc_fence_after_sync();
         {   // mask epilogue (one exponential per element, shared with gdn_prepare_kernel): thread = row i = TMEM lane
@@ -189,10 +188,10 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         // both heads are done with their A matrices (the stacked operand lies over head a's) and with the raw
         // products in tensor memory (W goes through the same columns)
         __syncthreads();
-        if (htid < kChunk)   // T' = T diag(beta e^gamma): rows 64 h .. 64 h + 63 of the stacked operand
-            prep_store_scaled_T_row(Tm, ps.eg, i, sm + QSmem::OP, h * 64 + i);
-        else                 // T'' = T diag(beta), as it is, for the chain's V^T T''^T
-            prep_store_scaled_T_row_plain(Tm, ps.bet, i, ws.U + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
+        // T' = T diag(beta e^gamma) (rows 64 h .. 64 h + 63 of the stacked operand) and T'' = T diag(beta) (as it is, for
+        // the chain's V^T T''^T): every thread reads half a row of T once and writes both
+        prep_store_T_half_row_both(Tm, ps.eg, ps.bet, i, htid >> 6, sm + QSmem::OP, h * 64 + i,
+                                   ws.U + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
         fence_proxy_async_smem();
         __syncthreads();
         GDN_PHASE(5)

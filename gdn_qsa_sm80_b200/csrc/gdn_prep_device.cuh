@@ -334,8 +334,9 @@ __device__ __forceinline__ void prep_mask_row_P(const PrepScratch& ps, bool l2no
 // Everything up to the two 32x32 diagonal blocks involves only 32 consecutive rows, so ONE WARP does it for the rows
 // it owns with no CTA-level barrier (prep_invert_diag32); only the last level crosses (prep_invert_level2).
 
-// One warp: the 32x32 diagonal block p (rows and columns 32p .. 32p+31) of T.  Needs rows 32p .. 32p+31 of `As`
-// visible to the warp (after the warp's own writes a __syncwarp is enough).  `y`: 448 floats of scratch of its own.
+// One warp: the 32x32 diagonal block p (rows and columns 32p .. 32p+31) of T, zeros above its diagonal included.
+// Needs rows 32p .. 32p+31 of `As` visible to the warp (after the warp's own writes a __syncwarp is enough).
+// `y`: 448 floats of scratch of its own.
 __device__ __forceinline__ void prep_invert_diag32(const float* As, float* Tm, float* y, int p, int lane) {
     {   // four 8x8 diagonal blocks: lane = (block, column), forward substitution in registers
         const int blk = 4 * p + (lane >> 3), c = lane & 7;
@@ -363,9 +364,16 @@ __device__ __forceinline__ void prep_invert_diag32(const float* As, float* Tm, f
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) Tm[(8 * blk + i) * kSolveStride + 8 * blk + c] = x[i];
-        // zeros in the upper-right 8x8 of the two 16x16 diagonal blocks (one float4 per lane)
+        // zeros in the upper-right 8x8 of the two 16x16 diagonal blocks (one float4 per lane) ...
         const int b16 = 2 * p + (lane >> 4), r = (lane >> 1) & 7, q = lane & 1;
         *reinterpret_cast<float4*>(Tm + (16 * b16 + r) * kSolveStride + 16 * b16 + 8 + 4 * q) = make_float4(0.f, 0.f, 0.f, 0.f);
+        // ... and in the upper-right 16x16 of the 32x32 block (two per lane; rows r0 and r0 + 4 share a quarter-warp, which
+        // keeps the 16-byte stores off each other's banks)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int q4 = lane & 3, rr = ((lane >> 2) & 1) * 4 + (lane >> 3) + 8 * e;
+            *reinterpret_cast<float4*>(Tm + (32 * p + rr) * kSolveStride + 32 * p + 16 + 4 * q4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
     __syncwarp();
     {   // 8 -> 16 in fp32: X21 = -X22 (A21 X11).  lane = (16-block, row r, four columns c0 ..) of the 8x8 result
@@ -519,6 +527,41 @@ __device__ __forceinline__ void prep_store_scaled_T_row(const float* Tm, const f
         pk.z = pack_bf16x2(t1.x * f1.x, t1.y * f1.y);
         pk.w = pack_bf16x2(t1.z * f1.z, t1.w * f1.w);
         *reinterpret_cast<uint4*>(tile + swz_chunk_offset<128>(dst_row, ch)) = pk;
+    }
+}
+
+// Columns [32 hh, 32 hh + 32) of row i of T, read once, as bf16 into BOTH consumers: T diag(fa) into row `dst_row` of
+// a 128-byte-swizzled K-major tile and T diag(fb) into a plain row of 64 values in global memory.  The block of T
+// above its two 32x32 diagonal blocks (rows 0-31, columns 32-63) is zero by definition and is not read, so that
+// part of `Tm` need not be defined.  hh and i < 32 must be uniform over a warp.
+__device__ __forceinline__ void prep_store_T_half_row_both(const float* Tm, const float* fa, const float* fb, int i, int hh,
+                                                           uint8_t* tile, uint32_t dst_row, __nv_bfloat16* grow) {
+    if (hh == 1 && i < 32) {
+#pragma unroll
+        for (int ch = 4; ch < 8; ++ch) {
+            *reinterpret_cast<uint4*>(tile + swz_chunk_offset<128>(dst_row, ch)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(grow + ch * 8) = make_uint4(0, 0, 0, 0);
+        }
+        return;
+    }
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+        const int ch = 4 * hh + c4;
+        const float4 t0 = *reinterpret_cast<const float4*>(Tm + i * kSolveStride + ch * 8);
+        const float4 t1 = *reinterpret_cast<const float4*>(Tm + i * kSolveStride + ch * 8 + 4);
+        const float4 a0 = *reinterpret_cast<const float4*>(fa + ch * 8), a1 = *reinterpret_cast<const float4*>(fa + ch * 8 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(fb + ch * 8), b1 = *reinterpret_cast<const float4*>(fb + ch * 8 + 4);
+        uint4 pa, pb;
+        pa.x = pack_bf16x2(t0.x * a0.x, t0.y * a0.y);
+        pa.y = pack_bf16x2(t0.z * a0.z, t0.w * a0.w);
+        pa.z = pack_bf16x2(t1.x * a1.x, t1.y * a1.y);
+        pa.w = pack_bf16x2(t1.z * a1.z, t1.w * a1.w);
+        pb.x = pack_bf16x2(t0.x * b0.x, t0.y * b0.y);
+        pb.y = pack_bf16x2(t0.z * b0.z, t0.w * b0.w);
+        pb.z = pack_bf16x2(t1.x * b1.x, t1.y * b1.y);
+        pb.w = pack_bf16x2(t1.z * b1.z, t1.w * b1.w);
+        *reinterpret_cast<uint4*>(tile + swz_chunk_offset<128>(dst_row, ch)) = pa;
+        *reinterpret_cast<uint4*>(grow + ch * 8) = pb;
     }
 }
 
