@@ -167,7 +167,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 // the 32 x 32 diagonal block of T over this warp's own rows needs nobody else: no barrier, and it runs
                 // while the other warps are still in their part of the mask epilogue
                 __syncwarp();
-                prep_invert_diag32(As, Tm, Yt + 512 * hwarp, hwarp, lane);
+                prep_invert_diag32(As, Tm, Yt + kDiagScratch * hwarp, hwarp, lane);
             } else {           // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
                 prep_mask_row_P(ps, p.l2norm != 0, scale0, tmem_addr(tmem, lane_base, 0), i, low_rows,
                                 ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);

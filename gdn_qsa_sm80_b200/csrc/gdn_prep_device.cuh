@@ -13,8 +13,12 @@ namespace gdn {
 
 constexpr int kSolveStride = 68;   // fp32 row stride of the 64x64 solve matrices: 16-byte aligned rows,
                                    // and 68 = 4 (mod 32) spreads rows over banks for row-wise and fragment reads
-constexpr int kY1Stride = 20;      // row stride of the 16-column temporaries of merge level 1
-constexpr int kY2Stride = 36;      // row stride of the 32-column temporary of merge level 2
+// row strides of the temporaries of merge levels 1 (16 columns) and 2 (32 columns): 40 = 8 (mod 32) keeps both the
+// B-fragment reads (bank 8 t + g) and the accumulator-fragment stores of a half-warp off each other's banks
+constexpr int kY1Stride = 40;
+constexpr int kY2Stride = 40;
+constexpr int kDiagScratch = 16 * kY1Stride;   // floats of scratch one warp needs in prep_invert_diag32
+static_assert(2 * kDiagScratch <= 32 * kY2Stride, "the two warps' scratch must fit the buffer sized for merge level 2");
 
 struct alignas(16) PrepScratch {
     float gam[kChunk];        // gamma_j * log2(e): inclusive cumsum of the log gate inside the chunk
@@ -336,7 +340,7 @@ __device__ __forceinline__ void prep_mask_row_P(const PrepScratch& ps, bool l2no
 
 // One warp: the 32x32 diagonal block p (rows and columns 32p .. 32p+31) of T, zeros above its diagonal included.
 // Needs rows 32p .. 32p+31 of `As` visible to the warp (after the warp's own writes a __syncwarp is enough).
-// `y`: 448 floats of scratch of its own.
+// `y`: kDiagScratch floats of scratch of its own.
 __device__ __forceinline__ void prep_invert_diag32(const float* As, float* Tm, float* y, int p, int lane) {
     {   // four 8x8 diagonal blocks: lane = (block, column), forward substitution in registers
         const int blk = 4 * p + (lane >> 3), c = lane & 7;
@@ -414,7 +418,7 @@ __device__ __forceinline__ void prep_invert_diag32(const float* As, float* Tm, f
     }
     __syncwarp();
     {   // 16 -> 32 with TF32 warp MMAs: Y = A21 X11, X21 = -X22 Y (16 x 16 each)
-        float* y1 = y + 128;
+        float* y1 = y;   // the 8 -> 16 temporaries are dead
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
@@ -492,7 +496,7 @@ __device__ __forceinline__ void prep_invert_level2(const float* As, float* Tm, f
 __device__ __forceinline__ void prep_invert_unit_lower(const float* As, float* Tm, float* Yt,
                                                        PrepCtx ctx = PrepCtx::whole_cta()) {
     const int warp = ctx.tid >> 5, lane = ctx.tid & 31;
-    if (warp < 2) prep_invert_diag32(As, Tm, Yt + 512 * warp, warp, lane);
+    if (warp < 2) prep_invert_diag32(As, Tm, Yt + kDiagScratch * warp, warp, lane);
     ctx.sync();
     prep_invert_level2(As, Tm, Yt, ctx);
 }
