@@ -380,12 +380,14 @@ __device__ __forceinline__ void prep_invert_diag32(const float* As, float* Tm, f
         }
     }
     __syncwarp();
-    {   // 8 -> 16 in fp32: X21 = -X22 (A21 X11).  lane = (16-block, row r, four columns c0 ..) of the 8x8 result
-        const int b16 = 2 * p + (lane >> 4), r = (lane >> 1) & 7, c0 = 4 * (lane & 1);
+    {   // 8 -> 16 in fp32: X21 = -X22 (A21 X11).  lane = (16-block, row r, four columns c0 ..) of the 8x8 result; the
+        // block index is the lowest lane bit and the blocks' temporaries lie 72 floats apart, which keeps the lanes of a
+        // quarter-warp on different banks in the row reads, the temporaries' reads and the result's stores
+        const int b16 = 2 * p + (lane & 1), r = (lane >> 1) & 7, c0 = 4 * (lane >> 4);
         const float* a21 = As + (16 * b16 + 8 + r) * kSolveStride + 16 * b16;
         const float* x11 = Tm + (16 * b16) * kSolveStride + 16 * b16 + c0;
         const float* x22 = Tm + (16 * b16 + 8 + r) * kSolveStride + 16 * b16 + 8;
-        float* yb = y + 64 * (lane >> 4);
+        float* yb = y + 72 * (lane & 1);
         {
             const float4 a0 = *reinterpret_cast<const float4*>(a21), a1 = *reinterpret_cast<const float4*>(a21 + 4);
             const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
