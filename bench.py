@@ -48,6 +48,26 @@ DRAM_TRAFFIC = {
 }
 
 
+_RESULT_STREAM = None
+
+
+def keep_stdout_for_the_result():
+    """The contract is ONE JSON line on stdout.  Libraries write there too (NCCL prints its version banner on stdout at
+    some debug levels), so file descriptor 1 is pointed at stderr for the rest of the process and the result line goes
+    out through a private copy of the original descriptor."""
+    global _RESULT_STREAM
+    if _RESULT_STREAM is None:
+        sys.stdout.flush()
+        _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line):
+    out = _RESULT_STREAM or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def flops_per_token(Hq, Hv, C=64, D=128):
     """Dense products at 64x64x128 tile granularity; Q K^T and K K^T once per qk head."""
     return Hq * 4 * C * D + Hv * (6 * C * D + 6 * D * D)
@@ -213,13 +233,13 @@ def reference_arm(args, w, cfg, rank, world, local_rank):
             return
         base = cpu_arm(args.workload, args.seed, min_seconds=max(5.0, 0.5 * args.steps))
         cfg = dict(cfg, sharding=f"{world} independent batch elements, one per GPU, no communication")
-        print(json.dumps({"impl": "reference", "reference_kind": f"cpu port ({why})", "metric": METRIC,
+        emit({"impl": "reference", "reference_kind": f"cpu port ({why})", "metric": METRIC,
                           "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
                           "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
                           "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
                           "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
                           "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                          "gpu_launches": 0}))
+                          "gpu_launches": 0})
         return
 
     import torch.distributed as dist
@@ -311,7 +331,7 @@ def reference_arm(args, w, cfg, rank, world, local_rank):
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_arm(args.workload, args.seed, min_seconds=max(5.0, 0.5 * args.steps))
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -509,14 +529,14 @@ def seq_parallel_arm(args, w, cfg, rank, world, dev):
     if rank == 0:
         cfg = dict(cfg, sharding=f"one sequence in {world} contiguous segments, boundary states by send/recv, mode "
                                  f"{args.seq_parallel}")
-        print(json.dumps({
+        emit({
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks.summary(),
             "e2e": None, "gpu_launches": int(launches), "step_ms": per_step,
             "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": load_peaks()[0]["bf16_tflops"] * world,
                          "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / (load_peaks()[0]["bf16_tflops"] * world),
-                         "traffic": None, "note": "whole job over all GPUs; algorithmic flops, redundant passes not counted"}}))
+                         "traffic": None, "note": "whole job over all GPUs; algorithmic flops, redundant passes not counted"}})
 
 
 def main():
@@ -543,6 +563,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    keep_stdout_for_the_result()
 
     from gdn_qsa_sm80_b200.synthetic import WORKLOADS
     w = WORKLOADS[args.workload]
@@ -823,7 +844,7 @@ def main():
         base = cpu_arm(args.workload, args.seed)
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         line["cpu_baseline"]["torch_config0"] = torch_config0_arm()
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
