@@ -32,8 +32,10 @@ _module = None
 
 
 def reference_root():
-    """Where the reference checkout is, or None (it is absent on a machine that only runs the built file)."""
-    for cand in (os.environ.get("GDN_REFERENCE_ROOT"), "/root/reference"):
+    """Where the reference checkout is, or None (it is absent on a machine that only runs the built file):
+    the environment variable GDN_REFERENCE_ROOT, else a directory `reference` beside this repository."""
+    beside = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    for cand in (os.environ.get("GDN_REFERENCE_ROOT"), beside):
         if cand and os.path.isdir(os.path.join(cand, "csrc", "gdn_chunk")):
             return cand
     return None
