@@ -27,12 +27,14 @@ struct QSmem {
     static constexpr uint32_t KQ = 0;                    // [K;Q]: 2 k-halves x 128 rows x 128 B (K rows 0-63, Q rows 64-127)
     static constexpr uint32_t YT = KQ + 8192;            // merge temporaries of head h at YT + h * 16384: Q's rows, dead after Q K^T
     static constexpr uint32_t AS = KQ + 32768;           // A fp32 64 x 68 of head h at AS + h * 17408 ...
-    static constexpr uint32_t OP = AS;                   // ... then the stacked bf16 operand [T'_a ; T'_b] (16 KB) over head a's A
+    static constexpr uint32_t OP = AS;                   // ... then the stacked bf16 operand [T'_a ; T'_b] (16 KB) over head a's A,
+                                                         //     and after the second product the P staging tiles of both heads there
+    static constexpr uint32_t T2S = AS + 17408;          // ... and the T'' staging tiles of both heads (16 KB) over head b's A
     static constexpr uint32_t TM = AS + 2 * 17408;       // T fp32 64 x 68 of head h at TM + h * 17408 ...
     static constexpr uint32_t STG = TM;                  // ... then the W staging tiles of both heads (32 KB)
     static constexpr uint32_t kBytes = TM + 2 * 17408;   // 102400
     static constexpr uint32_t kDynamic = kBytes + 1024;
-    static_assert(OP % 1024 == 0 && STG % 1024 == 0, "UMMA / TMA tiles must be 1024-byte aligned");
+    static_assert(OP % 1024 == 0 && STG % 1024 == 0 && T2S % 1024 == 0, "UMMA / TMA tiles must be 1024-byte aligned");
 };
 constexpr uint32_t kPairTmemCols = 128;   // [K;Q] K^T in the first 64, then W of both heads through all 128
 constexpr int kPairCtasPerSm = 2;
@@ -40,7 +42,8 @@ constexpr int kPairCtasPerSm = 2;
 template <bool GATE_F32>
 __global__ void __launch_bounds__(256, kPairCtasPerSm)
 gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                        const __grid_constant__ CUtensorMap tm_w, Problem p, Workspace ws, int NT, long long num_items) {
+                        const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_p,
+                        const __grid_constant__ CUtensorMap tm_t2, Problem p, Workspace ws, int NT, long long num_items) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sm_u32 = smem_u32(sm);
@@ -156,6 +159,11 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         GDN_PHASE(1)
 
         tc_fence_after_sync();
+        // Row i of P (warps 2, 3 of each half).  Rows written one per thread straight to global memory cost the LSU
+        // data pipe a wavefront per lane and store (a third of the kernel's wavefronts when P and T'' left that
+        // way); so P, like T'' and W, leaves through a swizzled staging tile and a TMA store.  No shared memory is
+        // free for the tile before the second product has read its operand, hence the wait in registers.
+        uint4 prow[8];
         {   // mask epilogue (one exponential per element, shared with gdn_prepare_kernel): thread = row i = TMEM lane
             const bool low_rows = (hwarp & 1) == 0;          // rows 0-31: columns 32-63 lie above the diagonal
             if (hwarp < 2) {   // A = tril(beta_i * decay * K K^T, -1), fp32, for the inverse
@@ -168,9 +176,8 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 // while the other warps are still in their part of the mask epilogue
                 __syncwarp();
                 prep_invert_diag32(As, Tm, Yt + kDiagScratch * hwarp, hwarp, lane);
-            } else {           // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
-                prep_mask_row_P(ps, p.l2norm != 0, scale0, tmem_addr(tmem, lane_base, 0), i, low_rows,
-                                ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
+            } else {           // P = tril(scale * decay * Q K^T), bf16: the row waits in registers for its staging tile
+                prep_mask_row_P_packed(ps, p.l2norm != 0, scale0, tmem_addr(tmem, lane_base, 0), i, low_rows, prow);
             }
         }
         GDN_PHASE(2)
@@ -190,8 +197,8 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         __syncthreads();
         // T' = T diag(beta e^gamma) (rows 64 h .. 64 h + 63 of the stacked operand) and T'' = T diag(beta) (as it is, for
         // the chain's V^T T''^T): every thread reads half a row of T once and writes both
-        prep_store_T_half_row_both(Tm, ps.eg, ps.bet, i, htid >> 6, sm + QSmem::OP, h * 64 + i,
-                                   ws.U + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
+        prep_store_T_half_row_tiles(Tm, ps.eg, ps.bet, i, htid >> 6, sm + QSmem::OP, h * 64 + i,
+                                    sm + QSmem::T2S + h * 8192, i);
         fence_proxy_async_smem();
         __syncthreads();
         GDN_PHASE(5)
@@ -206,6 +213,10 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 umma_bf16_ss(tmem, ad, bk, idesc_w, ks > 0);
             }
             umma_commit(&bar_mma);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)   // T'' of both heads; tid 0 is in half 0: tile = head a's
+                tma_store_2d(&tm_t2, sm + QSmem::T2S + hh * 8192, 0, static_cast<int>((tile + static_cast<size_t>(hh) * NT) * kChunk));
+            tma_store_commit();
         }
         ok = mbar_wait(&bar_mma, ph_mma, p.status, kDevTimeoutMma);
         ph_mma ^= 1;
@@ -243,6 +254,11 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 }
             }
         }
+        if (hwarp >= 2) {   // the P rows: staging tile of head h over the operand, which the second product has read
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4*>(sm + QSmem::OP + h * 8192 + swz_chunk_offset<128>(i, ch)) = prow[ch];
+        }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
@@ -252,6 +268,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 const int row0 = static_cast<int>((tile + static_cast<size_t>(hh) * NT) * kChunk);   // tid 0 is in half 0: tile = head a's
                 tma_store_2d(&tm_w, sm + QSmem::STG + hh * 16384, 0, row0);
                 tma_store_2d(&tm_w, sm + QSmem::STG + hh * 16384 + 8192, 64, row0);
+                tma_store_2d(&tm_p, sm + QSmem::OP + hh * 8192, 0, row0);
             }
             tma_store_commit();
         }
@@ -274,10 +291,16 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
 int launch_prepare_pair(const Problem& p, const Workspace& ws, cudaStream_t stream) {
     if (p.Hv % 2 || (p.Hv / p.Hq) % 2) return GDN_ERR_BAD_ARGUMENT;
-    alignas(64) CUtensorMap tq, tk, tv, tw, tp;
+    alignas(64) CUtensorMap tq, tk, tv, tw, tp, tt2;
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
     if (encode_workspace_maps(p, ws, &tw, &tp, nullptr, nullptr, 64)) return GDN_ERR_DRIVER;
     const int NT = (p.S + kChunk - 1) / kChunk;
+    {   // T'' = T diag(beta): [tiles * 64][64] bf16 at the start of the U array
+        const unsigned long long rows = static_cast<unsigned long long>(p.B) * p.Hv * NT * kChunk;
+        const unsigned long long d[2] = {64, rows}, sb[1] = {128};
+        const unsigned box[2] = {64, 64};
+        if (encode_tma(&tt2, ws.U, 2, 2, d, sb, box, 128)) return GDN_ERR_DRIVER;
+    }
     const long long items = static_cast<long long>(p.B) * (p.Hv / 2) * NT;
     const long long max_ctas = static_cast<long long>(kPairCtasPerSm) * sm_count();
     const unsigned grid = static_cast<unsigned>(items < max_ctas ? items : max_ctas);
@@ -285,7 +308,7 @@ int launch_prepare_pair(const Problem& p, const Workspace& ws, cudaStream_t stre
         const uint32_t smem = p.dbg == 4 ? 200 * 1024 : QSmem::kDynamic;   // dbg 4 (experiment): one CTA per SM
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return GDN_ERR_CUDA;
-        kernel<<<grid, 256, smem, stream>>>(tq, tk, tw, p, ws, NT, items);
+        kernel<<<grid, 256, smem, stream>>>(tq, tk, tw, tp, tt2, p, ws, NT, items);
         count_launch();
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };

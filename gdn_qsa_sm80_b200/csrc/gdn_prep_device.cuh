@@ -293,10 +293,10 @@ __device__ __forceinline__ float prep_bound_of_rows(const PrepScratch& ps, bool 
     return bound;
 }
 
-// Raw Q K^T row -> row i of P = tril(scale * decay * Q K^T), bf16, straight to the workspace (`prow`: 64 values).
+// Raw Q K^T row -> row i of P = tril(scale * decay * Q K^T) as 64 bf16 values in registers (eight 16-byte chunks).
 // The row factor (positive) travels in the exponent.
-__device__ __forceinline__ void prep_mask_row_P(const PrepScratch& ps, bool l2norm, float scale0, uint32_t trow, int i,
-                                                bool low_rows, __nv_bfloat16* prow) {
+__device__ __forceinline__ void prep_mask_row_P_packed(const PrepScratch& ps, bool l2norm, float scale0, uint32_t trow,
+                                                       int i, bool low_rows, uint4 (&pk)[8]) {
     const float* gcol = l2norm ? ps.ctab[0] : ps.gam;
     const float gis = ps.gam[i] + __log2f(l2norm ? scale0 * ps.rn[kChunk + i] : scale0);
     uint32_t r[32];
@@ -304,7 +304,7 @@ __device__ __forceinline__ void prep_mask_row_P(const PrepScratch& ps, bool l2no
     for (int half = 0; half < 2; ++half) {
         if (half == 1 && low_rows) {               // above the diagonal: zeros
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(prow + 32 + 8 * ch) = make_uint4(0, 0, 0, 0);
+            for (int ch = 0; ch < 4; ++ch) pk[4 + ch] = make_uint4(0, 0, 0, 0);
             break;
         }
         tmem_ld_x32(trow + half * 32, r);
@@ -320,14 +320,21 @@ __device__ __forceinline__ void prep_mask_row_P(const PrepScratch& ps, bool l2no
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-            uint4 pk;
-            pk.x = pack_bf16x2(x[8 * ch + 0], x[8 * ch + 1]);
-            pk.y = pack_bf16x2(x[8 * ch + 2], x[8 * ch + 3]);
-            pk.z = pack_bf16x2(x[8 * ch + 4], x[8 * ch + 5]);
-            pk.w = pack_bf16x2(x[8 * ch + 6], x[8 * ch + 7]);
-            *reinterpret_cast<uint4*>(prow + half * 32 + 8 * ch) = pk;
+            pk[4 * half + ch].x = pack_bf16x2(x[8 * ch + 0], x[8 * ch + 1]);
+            pk[4 * half + ch].y = pack_bf16x2(x[8 * ch + 2], x[8 * ch + 3]);
+            pk[4 * half + ch].z = pack_bf16x2(x[8 * ch + 4], x[8 * ch + 5]);
+            pk[4 * half + ch].w = pack_bf16x2(x[8 * ch + 6], x[8 * ch + 7]);
         }
     }
+}
+
+// The same row, straight to the workspace (`prow`: 64 values).
+__device__ __forceinline__ void prep_mask_row_P(const PrepScratch& ps, bool l2norm, float scale0, uint32_t trow, int i,
+                                                bool low_rows, __nv_bfloat16* prow) {
+    uint4 pk[8];
+    prep_mask_row_P_packed(ps, l2norm, scale0, trow, i, low_rows, pk);
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(prow + 8 * ch) = pk[ch];
 }
 
 // Blocked inversion of T = (I + A)^-1 for the strictly lower-triangular 64x64 A in `As` (fp32, row stride
@@ -568,6 +575,39 @@ __device__ __forceinline__ void prep_store_T_half_row_both(const float* Tm, cons
         pb.w = pack_bf16x2(t1.z * b1.z, t1.w * b1.w);
         *reinterpret_cast<uint4*>(tile + swz_chunk_offset<128>(dst_row, ch)) = pa;
         *reinterpret_cast<uint4*>(grow + ch * 8) = pb;
+    }
+}
+
+// The same with T diag(fb) into row `row_b` of a second 128-byte-swizzled tile in shared memory (a staging tile that a
+// TMA store takes to global memory: a row per thread written straight to global memory costs a wavefront per lane).
+__device__ __forceinline__ void prep_store_T_half_row_tiles(const float* Tm, const float* fa, const float* fb, int i, int hh,
+                                                            uint8_t* tile_a, uint32_t row_a, uint8_t* tile_b, uint32_t row_b) {
+    if (hh == 1 && i < 32) {
+#pragma unroll
+        for (int ch = 4; ch < 8; ++ch) {
+            *reinterpret_cast<uint4*>(tile_a + swz_chunk_offset<128>(row_a, ch)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(tile_b + swz_chunk_offset<128>(row_b, ch)) = make_uint4(0, 0, 0, 0);
+        }
+        return;
+    }
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+        const int ch = 4 * hh + c4;
+        const float4 t0 = *reinterpret_cast<const float4*>(Tm + i * kSolveStride + ch * 8);
+        const float4 t1 = *reinterpret_cast<const float4*>(Tm + i * kSolveStride + ch * 8 + 4);
+        const float4 a0 = *reinterpret_cast<const float4*>(fa + ch * 8), a1 = *reinterpret_cast<const float4*>(fa + ch * 8 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(fb + ch * 8), b1 = *reinterpret_cast<const float4*>(fb + ch * 8 + 4);
+        uint4 pa, pb;
+        pa.x = pack_bf16x2(t0.x * a0.x, t0.y * a0.y);
+        pa.y = pack_bf16x2(t0.z * a0.z, t0.w * a0.w);
+        pa.z = pack_bf16x2(t1.x * a1.x, t1.y * a1.y);
+        pa.w = pack_bf16x2(t1.z * a1.z, t1.w * a1.w);
+        pb.x = pack_bf16x2(t0.x * b0.x, t0.y * b0.y);
+        pb.y = pack_bf16x2(t0.z * b0.z, t0.w * b0.w);
+        pb.z = pack_bf16x2(t1.x * b1.x, t1.y * b1.y);
+        pb.w = pack_bf16x2(t1.z * b1.z, t1.w * b1.w);
+        *reinterpret_cast<uint4*>(tile_a + swz_chunk_offset<128>(row_a, ch)) = pa;
+        *reinterpret_cast<uint4*>(tile_b + swz_chunk_offset<128>(row_b, ch)) = pb;
     }
 }
 
