@@ -236,15 +236,13 @@ int forward_device(const void* q, const void* k, const void* v, const void* g, c
     if (path == GDN_PATH_DECODE || (path == GDN_PATH_AUTO && S <= kDecodeMaxTokens))
         return then_gate(launch_decode(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA);
     if (path == GDN_PATH_SIMT) return then_gate(launch_simt(p, stream) == cudaSuccess ? GDN_OK : GDN_ERR_CUDA);
-    // Automatic choice, by shape alone.  Few short sequences: the single-launch kernel whose four 32-column CTAs per
-    // head share the prepare work (2048 tokens, 32 sequences: 0.080 ms).  Everything else: the prepare kernel and the
-    // transposed chain (one CTA per head, state-dependent operands in tensor memory), which splits long sequences
-    // into segments when there are too few of them to fill the GPU.  Measured on one B200 against the earlier
-    // arrangements (64-column chain CTAs; single launch with dedicated chain SMs): 8192 tokens x 32 sequences 0.197 ms
-    // against 0.241; 512 sequences x 2048 tokens 0.63 against 0.75; 2048 x 4096 4.6 against 5.6; one 131072-token
-    // sequence x 32 heads 2.5 against 3.9.
+    // Automatic choice, by shape alone.  Few short sequences (up to 1024 tokens): the single-launch kernel whose four
+    // 32-column CTAs per head share the prepare work.  Everything else: the prepare kernel and the transposed chain
+    // (one CTA per head, state-dependent operands in tensor memory), which splits long sequences into segments when
+    // there are too few of them to fill the GPU.  Measured on one B200, 32 sequences, single launch against the two
+    // kernels: 512 tokens 0.036 / 0.037 ms, 1024 tokens 0.050 / 0.057, 2048 tokens 0.084 / 0.074.
     const bool automatic = path == GDN_PATH_AUTO;
-    if (automatic) path = (S <= 2048 && coop_supported(p)) ? GDN_PATH_COOP : GDN_PATH_TWOPASS_T;
+    if (automatic) path = (S <= 1024 && coop_supported(p)) ? GDN_PATH_COOP : GDN_PATH_TWOPASS_T;
     int nv;
     if (path == GDN_PATH_TWOPASS_NV32) nv = 32;
     else nv = 64;

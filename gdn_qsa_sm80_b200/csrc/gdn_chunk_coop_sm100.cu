@@ -13,7 +13,7 @@
 //
 // Roles: NV = 32.  Every CTA is a chain CTA (4 per head) plus one prepare group that prepares every fourth chunk
 // of its own head.  12 warps: 0-3 chain epilogues (warp 2 lane 0 issues D3/D5), 4 TMA producer, 5 issues D4,
-// 6 publisher, 8-11 prepare group.  Needs 4*B*Hv <= #SMs.  Used for short sequences (up to 2048 tokens); longer ones
+// 6 publisher, 8-11 prepare group.  Needs 4*B*Hv <= #SMs.  Used for short sequences (up to 1024 tokens); longer ones
 // and larger batches take the prepare kernel and the transposed chain.
 //
 // All CTAs must be resident together (one CTA per SM because of its shared memory): the kernel is launched

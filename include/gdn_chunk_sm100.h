@@ -31,7 +31,7 @@ extern "C" {
 #define GDN_GATE_F32 1
 
 /* execution path */
-#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; COOP when S <= 2048 and 4*B*Hv <= #SMs; else TWOPASS_T     */
+#define GDN_PATH_AUTO 0          /* DECODE when S <= 8; COOP when S <= 1024 and 4*B*Hv <= #SMs; else TWOPASS_T     */
 #define GDN_PATH_SIMT 1          /* token-by-token fp32 kernel on CUDA cores (exact; slow; for checks) */
                                  /* (values 2, 3 and 10 belonged to kernels that have been removed)    */
 #define GDN_PATH_TWOPASS_NV64 4  /* prepare kernel + chain kernel, 64 value columns per chain CTA    */
