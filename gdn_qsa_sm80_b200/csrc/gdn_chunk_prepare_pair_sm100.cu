@@ -8,6 +8,8 @@
 // chain computes U^T = V^T T''^T itself from the raw V tile.  Per head and chunk the workspace receives
 //   W [64][128] bf16,  P [64][64] bf16,  T'' [64][64] bf16 (at the start of the U array),  the per-token factors and
 //   the two scalars of the decay bound (sum of g, max beta |k|^2).
+// W, P and T'' all leave through 128-byte-swizzled staging tiles and TMA stores (rows stored one per thread straight to
+// global memory cost the LSU data pipe, this kernel's busiest unit, a wavefront per lane).
 // Same math and the same device helpers as gdn_prepare_kernel (gdn_chunk_prepare_sm100.cu), which remains the
 // producer for an odd number of value heads per qk head and for the kernels that read U from the workspace.
 // Stands in for the reference's gdn_prepare_kernel (csrc/gdn_chunk/gdn_kernel.cu:343-710).
