@@ -43,12 +43,15 @@ constexpr uint32_t kPrepTmemCols = 128;
 constexpr int kPrepCtasPerSm = 3;
 
 // WITH_U = false: for the transposed chain, which forms U^T = V^T T''^T itself from the raw V tile: no V load, no
-// second product, no U tile; T'' = T diag(beta) (bf16, 64 x 64, row-major) goes to the workspace instead.
+// second product, no U tile; T'' = T diag(beta) (bf16, 64 x 64, row-major) goes to the workspace instead (tm_u then
+// describes T''), and both T'' and P leave through swizzled tiles and TMA stores: T'' from the operand's rows 64-127,
+// P from a tile in Q's place (rows stored one per thread straight to global memory cost a wavefront per lane).
 template <bool GATE_F32, bool WITH_U>
 __global__ void __launch_bounds__(128, kPrepCtasPerSm)
 gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
-                   const __grid_constant__ CUtensorMap tm_u, Problem p, Workspace ws, int NT, long long num_tiles) {
+                   const __grid_constant__ CUtensorMap tm_u, const __grid_constant__ CUtensorMap tm_p, Problem p,
+                   Workspace ws, int NT, long long num_tiles) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sm_u32 = smem_u32(sm);
@@ -177,13 +180,24 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     const float bound = prep_bound_of_rows(ps, p.l2norm != 0, i, ksq);
                     if ((tid & 31) == 0) ps.wsum[warp] = bound;   // the cumsum's slots are free again by now
                 }
-            } else {          // P = tril(scale * decay * Q K^T), bf16, straight to the workspace
+            } else if (WITH_U) {   // P = tril(scale * decay * Q K^T), bf16, straight to the workspace (V is taking Q's place)
                 prep_mask_row_P(ps, p.l2norm != 0, scale0, tmem_addr(tmem, lane_base, 0), i, low_rows,
                                 ws.P + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
+            } else {               // ... into a staging tile in the place of Q's first k-half (Q is dead, no V comes)
+                uint4 pk[8];
+                prep_mask_row_P_packed(ps, p.l2norm != 0, scale0, tmem_addr(tmem, lane_base, 0), i, low_rows, pk);
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch)
+                    *reinterpret_cast<uint4*>(sm + PSmem::KQ + 8192 + swz_chunk_offset<128>(i, ch)) = pk[ch];
+                fence_proxy_async_smem();
             }
         }
         tc_fence_before_sync();
         __syncthreads();
+        if (!WITH_U && tid == 0) {
+            tma_store_2d(&tm_p, sm + PSmem::KQ + 8192, 0, static_cast<int>(tile * kChunk));
+            tma_store_commit();
+        }
         if (ws.meta && tid == 0) {
             ws.meta[2 * tile] = ps.gam[kChunk - 1] * (1.f / kLog2e);
             ws.meta[2 * tile + 1] = fmaxf(ps.wsum[0], ps.wsum[1]);
@@ -195,13 +209,15 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
         {   // [T diag(beta e^gamma) ; T diag(beta)] as one 128-row K-major operand
             const int which = tid >> 6;
-            if (WITH_U || which == 0)
-                prep_store_scaled_T_row(Tm, which == 0 ? ps.eg : ps.bet, i, sm + PSmem::AS, which * 64 + i);   // A is dead
-            else   // T'' leaves as it is (operand rows 64-127 stay undefined: their product rows are never read)
-                prep_store_scaled_T_row_plain(Tm, ps.bet, i, ws.U + tile * (kChunk * kChunk) + static_cast<size_t>(i) * kChunk);
+            // without U, rows 64-127 are only the staging tile of T'' (their product rows are never read)
+            prep_store_scaled_T_row(Tm, which == 0 ? ps.eg : ps.bet, i, sm + PSmem::AS, which * 64 + i);   // A is dead
         }
         fence_proxy_async_smem();
         __syncthreads();
+        if (!WITH_U && tid == 0) {
+            tma_store_2d(&tm_u, sm + PSmem::AS + 8192, 0, static_cast<int>(tile * kChunk));
+            tma_store_commit();
+        }
         if (WITH_U) {
             ok = mbar_wait(&bar_tma, ph_tma, p.status, kDevTimeoutTma);   // V has landed
             ph_tma ^= 1;
@@ -271,7 +287,10 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         Tile nxt = cur;
         if (Ln < num_tiles) {
             nxt = decode(Ln);
-            if (tid == 0) issue_loads(nxt);
+            if (tid == 0) {
+                if (!WITH_U) tma_store_wait_read();   // the P tile in Q's place has been read
+                issue_loads(nxt);
+            }
             prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(nxt.b) * p.S + nxt.s0, nxt.hv, p.Hv,
                                       min(kChunk, p.S - nxt.s0), gv, bv, PrepCtx::whole_cta(), p.gate_act != 0);
         }
@@ -329,13 +348,19 @@ int launch_prepare(const Problem& p, const Workspace& ws, cudaStream_t stream, b
     if (encode_qkv_maps(p, &tq, &tk, &tv, 64)) return GDN_ERR_DRIVER;
     if (encode_workspace_maps(p, ws, &tw, &tp, &tu, nullptr, 64)) return GDN_ERR_DRIVER;
     const int NT = (p.S + kChunk - 1) / kChunk;
+    if (!with_u) {   // T'' = T diag(beta): [tiles * 64][64] bf16 at the start of the U array
+        const unsigned long long rows = static_cast<unsigned long long>(p.B) * p.Hv * NT * kChunk;
+        const unsigned long long d[2] = {64, rows}, sb[1] = {128};
+        const unsigned box[2] = {64, 64};
+        if (encode_tma(&tu, ws.U, 2, 2, d, sb, box, 128)) return GDN_ERR_DRIVER;
+    }
     const long long tiles = static_cast<long long>(p.B) * p.Hv * NT;
     const long long max_ctas = static_cast<long long>(kPrepCtasPerSm) * sm_count();
     const unsigned grid = static_cast<unsigned>(tiles < max_ctas ? tiles : max_ctas);
     auto go = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PSmem::kDynamic) != cudaSuccess)
             return GDN_ERR_CUDA;
-        kernel<<<grid, 128, PSmem::kDynamic, stream>>>(tq, tk, tv, tw, tu, p, ws, NT, tiles);
+        kernel<<<grid, 128, PSmem::kDynamic, stream>>>(tq, tk, tv, tw, tu, tp, p, ws, NT, tiles);
         count_launch();
         return cudaGetLastError() == cudaSuccess ? GDN_OK : GDN_ERR_CUDA;
     };
