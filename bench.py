@@ -818,6 +818,9 @@ def main():
                                        "achieved": fl_prep / (per_kernel["prepare_only"] * 1e-3) / 1e12,
                                        "frac": fl_prep / (per_kernel["prepare_only"] * 1e-3) / 1e12 / peaks["bf16_tflops"]},
                     "whole_step": whole}
+        if traffic:   # the same launch against the HBM roofline, at the DRAM bytes it really moves
+            roofline["traffic_hbm"] = {"achieved": traffic / k_s / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                       "frac": traffic / k_s / 1e9 / peaks["hbm_gbs"]}
     elif single_launch:
         # one kernel per step: its duration is the step's (CUDA events around the launch)
         traffic = DRAM_TRAFFIC.get((args.workload, "gdn_coop_kernel")) if world == 1 else None
