@@ -47,6 +47,7 @@ EXPORTS = (
     "gdn_chunk_host_arena_bytes",
     "gdn_rmsnorm_gated_sm100",
     "gdn_key_norm_sq_max_sm100",
+    "gdn_forgetting_horizon_sm100",
     "gdn_chunk_fwd_gated_sm100",
     "gdn_chunk_fwd_host_sm100",
     "gdn_chunk_fwd_sm100_noalloc",
@@ -91,6 +92,8 @@ def load() -> ctypes.CDLL:
     lib.gdn_chunk_fwd_host_sm100.restype = ci
     lib.gdn_key_norm_sq_max_sm100.argtypes = [vp, ctypes.c_longlong, vp, vp]
     lib.gdn_key_norm_sq_max_sm100.restype = ci
+    lib.gdn_forgetting_horizon_sm100.argtypes = [vp, vp, ci, ci, ci, ci, vp, vp, vp, vp]
+    lib.gdn_forgetting_horizon_sm100.restype = ci
     lib.gdn_rmsnorm_gated_sm100.argtypes = [vp, vp, vp, vp, ctypes.c_longlong, ctypes.c_float, vp]
     lib.gdn_rmsnorm_gated_sm100.restype = ci
     lib.gdn_chunk_fwd_gated_sm100.argtypes = [vp] * 8 + [ctypes.c_float, vp, vp, vp, sz] + [ci] * 6 + [ctypes.c_uint, vp]

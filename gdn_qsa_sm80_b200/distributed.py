@@ -83,16 +83,35 @@ def transfer_is_negligible(k, g, beta, use_qk_l2norm_in_kernel=False):
     return bool(ok.item())
 
 
-def forgetting_horizon(k, g, beta, chunk: int = 64, keys_are_normalized=False):
-    """Number of leading tokens p (a multiple of `chunk`, or None) after which the state the stretch started from
-    no longer shows in fp32: for every (batch, head) the sum of g over tokens [0, p) is below -115, so by the bound
-    of `transfer_is_negligible` the transfer matrix of [0, t) vanishes for every t >= p.  Outputs at tokens >= p and
-    the final state are then the same whatever the initial state was.  None when there is no such p inside the
-    stretch or the premise (0 <= beta |k|^2 <= 2, g <= 0) fails.  keys_are_normalized=True skips the pass over k
-    (for callers whose keys are L2-normalised by construction, or normalised inside the kernels)."""
+def _horizon_from(first: int, ok: int, S: int, chunk: int):
+    if not ok:
+        return None
+    p = (first + 1) * chunk                                             # chunks [0, first] are needed
+    return p if p < S else None
+
+
+def forgetting_horizon_launch(k, g, beta, chunk: int = 64, keys_are_normalized=False):
+    """Enqueues the computation of `forgetting_horizon` on the current stream and returns a handle for
+    `forgetting_horizon_read`; nothing is read on the host.  On CUDA tensors this is the library's two small kernels
+    (plus its pass over k unless keys_are_normalized); elsewhere a few torch reductions."""
     S = g.shape[1]
     if g.numel() == 0:
         return None
+    if (g.is_cuda and chunk == 64 and g.is_contiguous() and beta.is_contiguous() and g.dtype == beta.dtype
+            and g.dtype in (torch.float32, torch.bfloat16)):
+        from . import _lib
+        B, Hv = g.shape[0], g.shape[2]
+        nt = (S + chunk - 1) // chunk
+        kk = None if keys_are_normalized else _key_norm_sq_max(k)
+        scratch = torch.empty(B * nt * Hv + 2, dtype=torch.float32, device=g.device)
+        result = torch.empty(2, dtype=torch.int32, device=g.device)
+        with torch.cuda.device(g.device):
+            st = _lib.load().gdn_forgetting_horizon_sm100(
+                g.data_ptr(), beta.data_ptr(), 1 if g.dtype == torch.float32 else 0, B, S, Hv,
+                None if kk is None else kk.data_ptr(), scratch.data_ptr(), result.data_ptr(),
+                torch.cuda.current_stream(g.device).cuda_stream)
+        _lib.check(st, "gdn_forgetting_horizon_sm100")
+        return ("kernel", result, S, chunk, (scratch, kk))
     # sums per chunk first (p is a multiple of the chunk anyway), then a short scan over the chunks
     nt = (S + chunk - 1) // chunk
     gf = g.float()
@@ -108,11 +127,26 @@ def forgetting_horizon(k, g, beta, chunk: int = 64, keys_are_normalized=False):
         kk_max = _key_norm_sq_max(k)
     b_lo, b_hi = torch.aminmax(beta)
     ok = (kk_max * b_hi.float() <= 2.0) & (b_lo >= 0) & (g.max() <= 0)
-    first, ok = (int(x) for x in torch.stack([first.float(), ok.float()]).tolist())   # one host read
-    if not ok:
+    return ("torch", torch.stack([first.float(), ok.float()]), S, chunk, None)
+
+
+def forgetting_horizon_read(handle):
+    """The host read that completes `forgetting_horizon_launch` (waits for the stream the launch ran on)."""
+    if handle is None:
         return None
-    p = (first + 1) * chunk                                             # chunks [0, first] are needed
-    return p if p < S else None
+    _, result, S, chunk, _keep = handle
+    first, ok = (int(x) for x in result.tolist())                       # one host read
+    return _horizon_from(first, ok, S, chunk)
+
+
+def forgetting_horizon(k, g, beta, chunk: int = 64, keys_are_normalized=False):
+    """Number of leading tokens p (a multiple of `chunk`, or None) after which the state the stretch started from
+    no longer shows in fp32: for every (batch, head) the sum of g over tokens [0, p) is below -115, so by the bound
+    of `transfer_is_negligible` the transfer matrix of [0, t) vanishes for every t >= p.  Outputs at tokens >= p and
+    the final state are then the same whatever the initial state was.  None when there is no such p inside the
+    stretch or the premise (0 <= beta |k|^2 <= 2, g <= 0) fails.  keys_are_normalized=True skips the pass over k
+    (for callers whose keys are L2-normalised by construction, or normalised inside the kernels)."""
+    return forgetting_horizon_read(forgetting_horizon_launch(k, g, beta, chunk, keys_are_normalized))
 
 
 @dataclass(frozen=True)
@@ -235,19 +269,24 @@ def sequence_parallel_forward(q, k, v, g, beta, initial_state=None, group=None, 
         if forwards:
             send_state(s_fin)
         return out, s_fin
-    # pass A: this segment from a zero state (outputs, and B_seg = its final state), on every rank at the same time
-    inputs_ready = torch.cuda.current_stream(dev).record_event() if v.is_cuda else None
-    out, b_seg = compute(q, k, v, g, beta, None)
-    p = None
+    # The bound's reductions go first, on a side stream (they wait for the inputs only), so that they run before
+    # pass A fills the GPU; their host read comes after pass A has been enqueued and returns while it executes.
+    handle = None
     if decay_early_out and v.is_cuda:
-        # the bound's reductions and their host read run on a side stream while pass A, enqueued above, executes
-        # (the side stream waits for the inputs only, not for pass A)
+        inputs_ready = torch.cuda.current_stream(dev).record_event()
         side = _side_stream(dev)
         side.wait_event(inputs_ready)
         with torch.cuda.stream(side):
-            p = forgetting_horizon(k, g, beta, keys_are_normalized=keys_are_normalized)
+            handle = forgetting_horizon_launch(k, g, beta, keys_are_normalized=keys_are_normalized)
     elif decay_early_out:
-        p = forgetting_horizon(k, g, beta, keys_are_normalized=keys_are_normalized)
+        handle = forgetting_horizon_launch(k, g, beta, keys_are_normalized=keys_are_normalized)
+    # pass A: this segment from a zero state (outputs, and B_seg = its final state), on every rank at the same time
+    out, b_seg = compute(q, k, v, g, beta, None)
+    if decay_early_out and v.is_cuda:
+        with torch.cuda.stream(_side_stream(dev)):       # the copy to the host must not queue behind pass A
+            p = forgetting_horizon_read(handle)
+    else:
+        p = forgetting_horizon_read(handle)
     if p is not None:
         if forwards:
             send_state(b_seg)       # the outgoing state does not depend on the incoming one

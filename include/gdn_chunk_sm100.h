@@ -169,6 +169,18 @@ int gdn_chunk_fwd_gated_sm100(const void* q, const void* k, const void* v, const
 int gdn_key_norm_sq_max_sm100(const void* k, long long n_rows, float* out_max, void* stream);
 
 /*
+ * After how many leading 64-token chunks has every (batch, value head) of the stretch g, beta [B][S][Hv] (gate_dtype
+ * as in gdn_chunk_fwd_sm100) forgotten the state it started from: result[0] (device) = the first chunk c with
+ * sum_{t < 64 (c + 1)} g < -115 for all b, h, or ceil(S/64) if there is none; result[1] = 1 when the premise of the
+ * bound holds (g <= 0, beta >= 0, max beta * *kk_max <= 2; kk_max = NULL stands for keys of unit norm, e.g. from
+ * gdn_key_norm_sq_max_sm100 otherwise).  scratch: B * ceil(S/64) * Hv + 2 floats of device memory.  Two small
+ * launches on `stream`, no wait.  Used by the sequence-parallel driver to let a rank leave the serial ripple; the
+ * reference's counterpart is its measured reset test (csrc/gdn_chunk/gdn_scan_stage3_reset.cu:22-54).
+ */
+int gdn_forgetting_horizon_sm100(const void* g, const void* beta, int gate_dtype, int B, int S, int Hv,
+                                 const float* kk_max, float* scratch, int* result, void* stream);
+
+/*
  * Second level of the two-level chunk scan.  A [n_seq][G][128][128] and Bm (same shape), fp32: group g
  * of sequence s maps its incoming state to its outgoing state by S_out = A S_in + Bm.  Writes the
  * state every group starts from into s_in [n_seq][G][128][128] and the state after the last group
