@@ -209,9 +209,14 @@ int launch_chain_t(const Problem& p, const Workspace& ws, cudaStream_t stream) {
         const bool paired = (p.Hv / p.Hq) % 2 == 0 && p.Hv % 2 == 0 && p.dbg != 5;
         cfg.numAttrs = paired ? 2 : 1;
         cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tq, tk, tv, tw, tp, tt2, p, ws, L);
-        if (e != cudaSuccess && paired) {   // a context that cannot place the pairs: plain launch
+        if (e != cudaSuccess && paired) {   // a context that cannot place the pairs: no clusters
             (void)cudaGetLastError();
             cfg.numAttrs = 1;
+            e = cudaLaunchKernelEx(&cfg, kernel, tq, tk, tv, tw, tp, tt2, p, ws, L);
+        }
+        if (e != cudaSuccess) {             // ... or no dependent launch either: an ordinary launch (the kernel's wait is a no-op then)
+            (void)cudaGetLastError();
+            cfg.numAttrs = 0;
             e = cudaLaunchKernelEx(&cfg, kernel, tq, tk, tv, tw, tp, tt2, p, ws, L);
         }
         count_launch();
