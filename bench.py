@@ -680,6 +680,13 @@ def main():
                 gdn_chunk_host(host[0], host[1], host[2], host[3], host[4], initial_state=host[5], out=outs[i % 2],
                                final_state_out=sts[i % 2], synchronize=False, arena_slot=1 + i % 2)
 
+        def e2e_piped2_whole(i):
+            # two calls in flight, each as ONE segment: the other call's copies fill this call's gaps, and fewer,
+            # larger copies use the link better than a call's own segments do
+            with torch.cuda.stream(side[i % 2]):
+                gdn_chunk_host(host[0], host[1], host[2], host[3], host[4], initial_state=host[5], out=outs[i % 2],
+                               final_state_out=sts[i % 2], synchronize=False, arena_slot=1 + i % 2, seg_tokens=w.S)
+
         n_e2e = max(4, min(args.steps, 10))
 
         def time_e2e(fn):
@@ -707,6 +714,7 @@ def main():
         if args.path == "auto":
             modes["gdn_chunk_host, one call at a time"] = time_e2e(e2e_piped)
             modes["gdn_chunk_host, two calls in flight"] = time_e2e(e2e_piped2)
+            modes["gdn_chunk_host, two calls in flight, one segment each"] = time_e2e(e2e_piped2_whole)
         best = max(modes, key=modes.get)
         step_s = total_tokens / modes[best] / world          # seconds per step and rank at the best mode
         ceil_s = link_ceiling([t for t in host if t is not None], [out_host, st_host], dev, world)

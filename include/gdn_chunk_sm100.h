@@ -127,7 +127,8 @@ int gdn_chunk_fwd_sm100_ex(const void* q, const void* k, const void* v, const vo
  * start of the arena collects the bounded-wait reports of all segments (gdn_chunk_read_status(arena, ...)).
  * Calls that share an arena must be issued on the same stream.  Calls with different arenas on different
  * streams may be in flight together: their kernels overlap the other call's copies, while the copies
- * themselves share one queue per direction and device (one internal stream each way).  After an error return
+ * themselves share one queue per direction and device (one internal stream each way); with two calls in flight one
+ * segment per call (seg_tokens = S) uses the link best, with one call at a time the default of four does.  After an error return
  * the caller's stream is still ordered behind every copy the call had enqueued.
  * flags as in gdn_chunk_fwd_sm100_ex.
  * Replaces what a caller of the reference writes around it by hand: `.cuda()` on every input, the operator,
