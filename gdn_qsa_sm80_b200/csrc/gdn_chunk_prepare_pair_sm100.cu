@@ -53,6 +53,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     __shared__ __align__(8) uint64_t bar_mma;
     __shared__ uint32_t tmem_slot;
     __shared__ __align__(16) PrepScratch ps2[2];
+    __shared__ float gates_b[2][kChunk];   // head b's log gate and update gate of the coming item, loaded by head a's half
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = tid >> 7;                       // which head of the pair this half of the CTA prepares
@@ -114,9 +115,36 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         tmem_alloc(&tmem_slot, kPairTmemCols);
         tmem_relinquish();
     }
-    float gv, bv;
-    prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(cur.b) * p.S + cur.s0, cur.hv, p.Hv,
-                              min(kChunk, p.S - cur.s0), gv, bv, ctx, p.gate_act != 0);
+    // The gates of the two heads of a pair lie side by side in memory: head a's half loads both with one 8-byte (fp32)
+    // or 4-byte (bf16) access per token and hands head b's over through shared memory at the top of the item (a token
+    // per lane, a row of heads apart: every access is a sector of its own, so two halves loading one head each
+    // fetched every sector twice).  Padding tokens: zeros, or (raw gates) what prep_activate_gates maps to zeros.
+    float gv, bv, gv_b = 0.f, bv_b = 0.f;
+    auto load_gates_of_pair = [&](const Item& x) {
+        if (h != 0 || htid >= kChunk) return;
+        const float pad = p.gate_act ? -INFINITY : 0.f;
+        gv = bv = gv_b = bv_b = pad;
+        if (htid < min(kChunk, p.S - x.s0)) {
+            const size_t idx = (static_cast<size_t>(x.b) * p.S + x.s0 + htid) * p.Hv + x.hv;   // x.hv: head a (even)
+            if (GATE_F32) {
+                const float2 g2 = *reinterpret_cast<const float2*>(static_cast<const float*>(p.g) + idx);
+                const float2 b2 = *reinterpret_cast<const float2*>(static_cast<const float*>(p.beta) + idx);
+                gv = g2.x; gv_b = g2.y; bv = b2.x; bv_b = b2.y;
+            } else {
+                const float2 g2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(static_cast<const __nv_bfloat16*>(p.g) + idx));
+                const float2 b2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(static_cast<const __nv_bfloat16*>(p.beta) + idx));
+                gv = g2.x; gv_b = g2.y; bv = b2.x; bv_b = b2.y;
+            }
+        }
+    };
+    auto hand_over_gates = [&]() {   // before the barrier at the top of the item they belong to
+        if (h == 0 && htid < kChunk) {
+            gates_b[0][htid] = gv_b;
+            gates_b[1][htid] = bv_b;
+        }
+    };
+    load_gates_of_pair(cur);
+    hand_over_gates();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -131,6 +159,10 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         ph_tma ^= 1;
         ok = __syncthreads_and(ok);   // also: every warp has left the previous item's accumulator
         if (!ok) break;
+        if (h == 1 && htid < kChunk) {
+            gv = gates_b[0][htid];
+            bv = gates_b[1][htid];
+        }
         GDN_PHASE(0)
 
         if (tid == 0) {   // raw K K^T (lanes 0-63) and Q K^T (lanes 64-127), shared by the two heads
@@ -233,8 +265,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         if (Ln < num_items) {
             nxt = decode(Ln);
             if (tid == 0) issue_loads(nxt);
-            prep_load_gates<GATE_F32>(p.g, p.beta, static_cast<size_t>(nxt.b) * p.S + nxt.s0, nxt.hv, p.Hv,
-                                      min(kChunk, p.S - nxt.s0), gv, bv, ctx, p.gate_act != 0);
+            load_gates_of_pair(nxt);
         }
         {   // W rows -> bf16 -> swizzled staging tiles in the T buffers (T fp32 is dead).  TMEM lanes 0-63 are head a's
             // rows, 64-127 head b's; warps 0-3 take columns 0-63, warps 4-7 columns 64-127.
@@ -274,6 +305,7 @@ gdn_prepare_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             }
             tma_store_commit();
         }
+        hand_over_gates();   // the next item's, loaded above: they have had the whole staging to arrive
         GDN_PHASE(7)
         ++prof_n;
         cur = nxt;
