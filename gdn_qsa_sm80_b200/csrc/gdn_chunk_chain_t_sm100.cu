@@ -192,7 +192,7 @@ int launch_chain_t(const Problem& p, const Workspace& ws, cudaStream_t stream) {
         // scheduled together and run in step, which keeps the second read of a tile close behind the first (with
         // many sequences the kernel is bound by HBM and L2 turns over every 20 microseconds); measured: 1 % off the
         // kernel with 2048 sequences, nothing lost elsewhere.  Nothing else of the cluster is used: no distributed
-        // shared memory, no multicast, no cluster barrier.
+        // shared memory, no cluster barrier, every CTA does its own loads.
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(p.Hv, p.B, gz);
         cfg.blockDim = dim3(chain_t::kThreads);
