@@ -68,6 +68,14 @@ def emit(line):
     out.flush()
 
 
+def queue_ahead(flush, n=4):
+    """A few untimed L2 flushes right after the barrier, before the first timed step: the GPU has work while the host
+    enqueues that step, so the CUDA events of the first step bracket device time like those of every later step
+    (where the host runs a step ahead anyway) and not the host's launch latency on an idle GPU."""
+    for _ in range(n):
+        flush.zero_()
+
+
 def flops_per_token(Hq, Hv, C=64, D=128):
     """Dense products at 64x64x128 tile granularity; Q K^T and K K^T once per qk head."""
     return Hq * 4 * C * D + Hv * (6 * C * D + 6 * D * D)
@@ -281,6 +289,7 @@ def reference_arm(args, w, cfg, rank, world, local_rank):
         step()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
+    queue_ahead(flush)
     with ClockSampler(local_rank) as clocks:
         for a, b in ev:
             flush.zero_()
@@ -628,6 +637,7 @@ def main():
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     launches0 = _lib.kernel_launches()
     barrier()
+    queue_ahead(flush)
     with ClockSampler(local_rank) as clocks:
         for a, b in ev:
             flush.zero_()
